@@ -439,6 +439,65 @@ CPM_API int cpm_gated_head_norm(const float* o, const float* gate, int64_t gate_
     return launch_status();
 }
 
+// The same over groups of ``group`` heads normed together (group = heads: all of a token's heads as one vector), with a
+// weight per channel of the group [group * dv] and the gate's activation chosen (0: SiLU, 1: sigmoid); one block per
+// (token, group).
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t gate_stride,
+                                        const float* __restrict__ weight, T* __restrict__ out, int heads, int dv, int group,
+                                        int gate_act, float eps) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int width = group * dv, groups = heads / group;
+    const int64_t t = blockIdx.x / groups;
+    const int g = blockIdx.x % groups;
+    const float* row = o + (t * heads + (int64_t)g * group) * dv;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+    const float f = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+    const float* gr = gate + t * gate_stride + (int64_t)g * width;
+    T* dst = out + (t * heads + (int64_t)g * group) * dv;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float a = gate_act == 1 ? sigmoid_acc(gr[c]) : silu_acc(gr[c]);
+        dst[c] = from_f32<T>(row[c] * f * weight[c] * a);
+    }
+}
+
+CPM_API int cpm_gated_group_norm(const float* o, const float* gate, int64_t gate_stride, const float* weight, void* out,
+                                 int n_tokens, int heads, int dv, int group, int gate_act, float eps, int dtype,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (heads < 1 || dv < 1 || group < 1 || heads % group || gate_act < 0 || gate_act > 1) return CPM_BAD_ARGUMENT;
+    const int width = group * dv;
+    const dim3 grid((unsigned)((int64_t)n_tokens * (heads / group))), block(width >= 2048 ? 256 : 128);
+    if (dtype == CPM_BF16)
+        cpm_launch(kLaunchNorm, gated_group_norm_kernel<bf16>, grid, block, 0, stream, o, gate, gate_stride, weight, (bf16*)out, heads,
+                   dv, group, gate_act, eps);
+    else
+        cpm_launch(kLaunchNorm, gated_group_norm_kernel<float>, grid, block, 0, stream, o, gate, gate_stride, weight, (float*)out,
+                   heads, dv, group, gate_act, eps);
+    return launch_status();
+}
+
+// In place on the first ``cols`` floats of every row (``stride`` floats apart): x <- x * sigmoid(x).
+__global__ void silu_columns_kernel(float* __restrict__ x, int64_t stride, int cols, int64_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float* p = x + (i / cols) * stride + i % cols;
+    *p = silu_acc(*p);
+}
+
+CPM_API int cpm_silu_columns(float* x, int64_t stride, int n_tokens, int cols, cudaStream_t stream) {
+    if (n_tokens <= 0 || cols <= 0) return CPM_OK;
+    if (stride < cols) return CPM_BAD_ARGUMENT;
+    const int64_t n = (int64_t)n_tokens * cols;
+    cpm_launch(kLaunchOther, silu_columns_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, stride, cols, n);
+    return launch_status();
+}
+
 // out = (rms(a) * wa + rms(b) * wb) / 2 over the model width: the join of two mixers that ran side by side.
 template <typename T>
 __global__ void dual_rmsnorm_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,

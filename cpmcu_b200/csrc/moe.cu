@@ -4,6 +4,8 @@
 // ``n_groups`` equal groups of neighbours, a group's score is its largest choice score, and only experts of the
 // ``keep`` best groups can be chosen (the others count as minus infinity); the ``top`` largest choice scores are
 // chosen, and their weights are the plain scores s, not renormalised.  Ties go to the lower index.
+// A second rule (``top_first``): the choice scores are the logits plus a bias, the ``top`` largest are chosen, and
+// their weights are the softmax over the chosen logits only.
 //
 // Products: the (token, choice) pairs are grouped by expert (counts, offsets, a list of pairs in expert order),
 // and tiles of 32 pairs of one expert times 64 output features run as blocks of one launch, whose grid is an upper
@@ -31,7 +33,8 @@ __device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
 // shared expert's raw gate.
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
                                  int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate,
-                                 int gate_col, int n_tokens, int E, int top, int n_groups, int keep) {
+                                 int gate_col, int n_tokens, int E, int top, int n_groups, int keep,
+                                 const float* __restrict__ bias, int top_first) {
     extern __shared__ float route_smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -42,6 +45,34 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const
     float* c = s + E;                                                 // choice scores
     float* gs = c + E;                                                // group scores
     const float* z = logits + (int64_t)t * ld;
+    if (top_first) {
+        // choice scores: logits + bias; weights: softmax over the chosen scores (the largest is the first chosen)
+        for (int e = lane; e < E; e += 32) c[e] = z[e] + (bias ? bias[e] : 0.f);
+        __syncwarp();
+        float first = 0.f, sum = 0.f;
+        for (int r = 0; r < top; ++r) {
+            ArgMax a{-INFINITY, 0x7fffffff};
+            for (int e = lane; e < E; e += 32) {
+                const float v = c[e];
+                if (!isnan(v)) a = better(a, ArgMax{v, e});
+            }
+            a = warp_argmax(a);
+            const int e = a.i < E ? a.i : 0;
+            if (r == 0) first = a.v;
+            const float ex = expf(a.v - first);
+            sum += ex;
+            if (lane == 0) {
+                chosen[(int64_t)t * top + r] = e;
+                weights[(int64_t)t * top + r] = ex;
+                c[e] = NAN;                               // taken
+            }
+            __syncwarp();
+        }
+        if (lane == 0)
+            for (int r = 0; r < top; ++r) weights[(int64_t)t * top + r] /= sum;
+        if (gate_col >= 0 && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-z[gate_col]));
+        return;
+    }
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
     m = warp_max(m);
@@ -427,15 +458,17 @@ CPM_API int cpm_set_moe_tensor_cores(int on) {
 }
 
 CPM_API int cpm_moe_route(const float* logits, int ld, const float* correction, int* chosen, float* weights, float* shared_gate,
-                          int gate_col, int n_tokens, int E, int top, int n_groups, int keep, cudaStream_t stream) {
+                          int gate_col, int n_tokens, int E, int top, int n_groups, int keep, const float* bias, int top_first,
+                          cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
+    if (!top_first && !correction) return CPM_BAD_ARGUMENT;
     if (E < 1 || E > 32 * kRouteMaxPerLane || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups ||
         top > keep * (E / n_groups))
         return CPM_BAD_ARGUMENT;
     const int warps = 4;
     const size_t smem = (size_t)warps * (2 * E + n_groups) * sizeof(float);
     cpm_launch(kLaunchOther, moe_route_kernel, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32), smem, stream, logits, ld,
-               correction, chosen, weights, shared_gate, gate_col, n_tokens, E, top, n_groups, keep);
+               correction, chosen, weights, shared_gate, gate_col, n_tokens, E, top, n_groups, keep, bias, top_first);
     return launch_status();
 }
 

@@ -87,6 +87,10 @@ class Model:
             n = self.blocks[e.layer].cache_needs()
             if needs[e.lane] is None or e.writes_cache:
                 needs[e.lane] = n
+        for e in self.schedule:
+            if not e.writes_cache and needs[e.lane] is not None and needs[e.lane].kv_heads:
+                # a run that only reads the lane may look further back than the run that writes it
+                needs[e.lane] = needs[e.lane].seen_through(self.blocks[e.layer].cache_needs().window)
         return [n if n is not None else CacheNeeds() for n in needs]
 
     # ---- forward ----

@@ -71,6 +71,12 @@ _SIGNATURES = {
     "cpm_sigmoid_power": [_P, _P, c_float, c_int, c_int, _P],
     "cpm_gated_head_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_dual_rmsnorm_mean": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_gated_group_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_silu_columns": [_P, c_int64, c_int, c_int, _P],
+    "cpm_qk_prepare_store": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_float, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_sink_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                   c_int, c_int, _P],
     "cpm_talking_attention": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_scale_heads_bf16": [_P, _P, _P, c_int, c_int, c_int, _P],
     "cpm_talk_mix_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
@@ -82,7 +88,7 @@ _SIGNATURES = {
                                              c_float, _P, c_int, c_int, _P],
     "cpm_set_moe_tensor_cores": [c_int],
     "cpm_set_recurrence_columns": [c_int],
-    "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "cpm_moe_group": [_P, c_int, c_int, _P, _P, _P],
     "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_moe_pair_product": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
@@ -91,8 +97,8 @@ _SIGNATURES = {
 }
 
 # source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file
-BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "latent_attention", "sparse",
-                "talking_attention")
+BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "latent_attention", "sink_attention",
+                "sparse", "talking_attention")
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None

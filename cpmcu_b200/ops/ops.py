@@ -860,6 +860,81 @@ class Ops:
                                            self.code, self._stream()), "gated_head_norm")
         return out
 
+    GATE_ACTIVATIONS = {"silu": 0, "sigmoid": 1}
+
+    def gated_group_norm(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
+                         gate_activation: str = "silu") -> torch.Tensor:
+        """As ``gated_head_norm`` with ``group`` heads normed together (``group`` = heads: all heads of a token as one
+        vector), weight fp32 [group * dv], and the gate passed through SiLU or the sigmoid."""
+        self._f32(o, "recurrence output")
+        self._f32(weight, "group norm weight")
+        n, heads, dv = o.shape
+        if gate.dtype != torch.float32 or gate.shape != (n, heads * dv) or gate.stride(1) != 1:
+            raise ValueError("gated_group_norm: the gate must be fp32 [tokens, heads*dv]")
+        if heads % group or weight.numel() != group * dv:
+            raise ValueError(f"gated_group_norm: {heads} heads in groups of {group} need a weight of {group * dv} numbers")
+        out = self.empty(n, heads * dv)
+        check(self.lib.cpm_gated_group_norm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), n, heads, dv, int(group),
+                                            self.GATE_ACTIVATIONS[gate_activation], float(eps), self.code, self._stream()),
+              "gated_group_norm")
+        return out
+
+    def silu_columns(self, x: torch.Tensor, cols: int) -> torch.Tensor:
+        """In place on fp32 rows: the first ``cols`` entries of every row pass through SiLU."""
+        if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or cols > x.shape[1]:
+            raise ValueError("silu_columns: needs fp32 rows with unit stride inside a row")
+        check(self.lib.cpm_silu_columns(_ptr(x), x.stride(0), x.shape[0], int(cols), self._stream()), "silu_columns")
+        return x
+
+    # ---- attention with capped scores, a window and a sink ----
+    def qk_prepare_store(self, ctx, proj: torch.Tensor, lane, n_heads: int, n_kv: int, d: int, dv: int,
+                         biases, inv_freq: Optional[torch.Tensor], rot_dim: int, unit_rms: bool, eps: float,
+                         has_kv: bool = True) -> torch.Tensor:
+        """proj fp32 [tokens, heads*d + kv*d + kv*dv] (or [tokens, heads*d] without ``has_kv``): adds the biases
+        (``biases`` = (q, k, v), fp32 or None each), rotates the first ``rot_dim`` channels of every q and k head
+        (pairs (i, i + rot_dim/2), angle position * inv_freq[i]), divides q and k heads by their root mean square
+        (``unit_rms``), stores k and v into the lane's pages and returns q [tokens, heads, d] in the compute dtype."""
+        self._f32(proj, "projections")
+        n = proj.shape[0]
+        if proj.shape[1] != n_heads * d + (n_kv * (d + dv) if has_kv else 0):
+            raise ValueError("qk_prepare_store: the projections' row size does not match the head counts")
+        if inv_freq is not None:
+            self._f32(inv_freq, "inv_freq")
+            if inv_freq.numel() != rot_dim // 2:
+                raise ValueError("inv_freq needs rot_dim/2 entries")
+        bq, bk, bv = biases
+        for b, what in ((bq, "q bias"), (bk, "k bias"), (bv, "v bias")):
+            if b is not None:
+                self._f32(b, what)
+        q = self.empty(n, n_heads, d)
+        check(self.lib.cpm_qk_prepare_store(_ptr(proj), proj.stride(0), _ptr(bq), _ptr(bk), _ptr(bv), _ptr(q),
+                                            _ptr(lane.k) if has_kv else None, _ptr(lane.v) if has_kv else None,
+                                            _ptr(ctx.positions), _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                            lane.page_table.shape[1], _ptr(inv_freq) if rot_dim else None, int(rot_dim),
+                                            1 if unit_rms else 0, float(eps), n, n_heads, n_kv, d, dv, 1 if has_kv else 0,
+                                            self.code, self._stream()), "qk_prepare_store")
+        return q
+
+    def sink_attention(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int = 0, cap: float = 0.0,
+                       sink: bool = True) -> torch.Tensor:
+        """q [tokens, heads, d] over the lane's cached keys and values -> [tokens, heads*dv]: scores times ``scale``, capped
+        by cap * tanh(s / cap) when ``cap`` > 0, keys 0 <= i - j < ``window`` (0: all before and at i), softmax with one
+        added to the denominator when ``sink``.  Picks the kernel."""
+        return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
+
+    def sink_attention_generic(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
+                               sink: bool) -> torch.Tensor:
+        """The kernel of every size and both precisions (one warp per token and head, fp32 arithmetic)."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        out = self.empty(n, n_heads * dv)
+        check(self.lib.cpm_sink_attention_generic(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(ctx.positions),
+                                                  _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                                  lane.page_table.shape[1], int(window), n, n_heads, n_kv, d, dv, float(scale),
+                                                  float(cap), 1 if sink else 0, self.code, self._stream()),
+              f"sink attention ({n_heads} heads, {d} / {dv})")
+        return out
+
     def dual_rmsnorm_mean(self, a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float) -> torch.Tensor:
         """(rms_norm(a) * wa + rms_norm(b) * wb) / 2 over the last axis, [tokens, hidden] in the compute dtype."""
         self._act(a, "left output")
@@ -948,18 +1023,27 @@ class Ops:
         return out
 
     # ---- routed experts ----
-    def moe_route(self, logits: torch.Tensor, correction: torch.Tensor, n_experts: int, top: int, n_groups: int, keep: int,
-                  gate_col: int = -1):
+    def moe_route(self, logits: torch.Tensor, correction: Optional[torch.Tensor], n_experts: int, top: int, n_groups: int, keep: int,
+                  gate_col: int = -1, bias: Optional[torch.Tensor] = None, top_first: bool = False):
         """logits fp32 [tokens, >= experts] -> (chosen int32 [tokens, top], weights fp32 [tokens, top], sigmoid of column
-        ``gate_col`` fp32 [tokens] or None)."""
+        ``gate_col`` fp32 [tokens] or None).  Default rule: softmax over all experts, choice by score + ``correction``
+        within the kept groups, weights the plain scores.  ``top_first``: choice by logit + ``bias`` (fp32 [experts] or
+        None), weights the softmax over the chosen logits only."""
         self._f32(logits, "router logits")
-        self._f32(correction, "router correction")
+        if top_first:
+            if bias is not None:
+                self._f32(bias, "router bias")
+            if n_groups != 1:
+                raise ValueError("moe_route: the rule that chooses first has no groups of experts")
+        else:
+            self._f32(correction, "router correction")
         n = logits.shape[0]
         chosen = self.empty(n, top, dtype=torch.int32)
         weights = self.empty(n, top, dtype=torch.float32)
         gate = self.empty(n, dtype=torch.float32) if gate_col >= 0 else None
         check(self.lib.cpm_moe_route(_ptr(logits), logits.shape[1], _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate),
-                                     int(gate_col), n, n_experts, top, n_groups, keep, self._stream()),
+                                     int(gate_col), n, n_experts, top, n_groups, keep, _ptr(bias), 1 if top_first else 0,
+                                     self._stream()),
               f"moe_route ({n_experts} experts, top {top})")
         return chosen, weights, gate
 

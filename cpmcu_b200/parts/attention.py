@@ -125,3 +125,95 @@ class GroupedQueryAttention(Mixer):
                         (lane.index, list(ctx.slots), ctx.token_seq.clone(), ctx.positions.clone(), block_list.clone()))
         out = ops.attention(ctx, q, lane, self.n_kv, self.scale, self.window, block_list, block_size)
         return ops.linear(out, self.w_o)
+
+
+@MIXERS.register("sink_window_attention")
+class SinkWindowAttention(Mixer):
+    """Grouped-query softmax attention over the paged cache with biased projections, unit-rms queries and keys, capped
+    scores, a sliding window and a sink:
+
+        q = Wq h + bq,  k = Wk h + bk,  v = Wv h + bv           (q, k heads of ``head_dim`` channels, v of ``value_dim``)
+        q, k <- position(q, k);   q, k <- x / sqrt(mean(x^2) + eps) per head          (``unit_rms``; no weight)
+        s(i, j) = q_i . k_j * softmax_scale;   s <- softcap * tanh(s / softcap)        (``softcap`` > 0)
+        j is seen by i when 0 <= i - j < window                                        (``window``; None: all j <= i)
+        p_j = exp(s_j) / (1 + sum_j' exp(s_j'))      (``sink``: a further key of score 0 without a value; else plain)
+        out = Wo [o_0 | o_1 | ...],  o_h = sum_j p_j v_kv(h)(j)
+
+    With ``own_kv`` False the layer has no key and value projections: it reads the lane another layer of equal head
+    counts and rotation wrote (keys as cached, after rotation and norm), with its own queries, window, cap and scale.
+    ``biases``: which of "q", "k", "v" have one (tensor name + ``names["bias"]``).  Biases, rotation, the unit rms,
+    scores and weights are 32-bit; keys and values live in the cache in the compute dtype.
+    """
+
+    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "bias": ".b"}
+
+    @property
+    def recordable_prompt(self) -> bool:
+        return bool(self.position.recordable_prompt)
+
+    def __init__(self, ops, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
+                 softmax_scale: float, position: PartSpec, eps: float, window: Optional[int] = None, softcap: float = 0.0,
+                 sink: bool = True, unit_rms: bool = True, biases=("q", "k", "v"), own_kv: bool = True, names=None):
+        super().__init__(ops)
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads cannot be grouped over {n_kv_heads} key-value heads")
+        if head_dim > 256 or value_dim > 256:
+            raise ValueError("sink_window_attention: the kernels take heads of up to 256 channels")
+        self.hidden_size, self.n_heads, self.n_kv = int(hidden_size), int(n_heads), int(n_kv_heads)
+        self.d, self.dv, self.scale, self.eps = int(head_dim), int(value_dim), float(softmax_scale), float(eps)
+        self.window = int(window) if window else 0
+        self.softcap, self.sink, self.unit_rms, self.own_kv = float(softcap or 0.0), bool(sink), bool(unit_rms), bool(own_kv)
+        self.biases = tuple(b for b in ("q", "k", "v") if b in tuple(biases) and (b == "q" or self.own_kv))
+        self.position = build_part(POSITIONS, position, ops)
+        self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
+        self.bias = {"q": None, "k": None, "v": None}
+
+    def _projections(self):
+        G, d, dv = self.n_kv, self.d, self.dv
+        return [("q", self.n_heads * d)] + ([("k", G * d), ("v", G * dv)] if self.own_kv else [])
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W = self.names, self.hidden_size
+        specs = {n["o"]: WeightSpec((W, self.n_heads * self.dv))}
+        for which, rows in self._projections():
+            specs[n[which]] = WeightSpec((rows, W))
+            if which in self.biases:
+                specs[n[which] + n["bias"]] = WeightSpec((rows,), "vector")
+        return specs
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in = self.ops.keep(torch.cat([tensors[n[which]] for which, _ in self._projections()], dim=0).contiguous())
+        self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
+        for which in self.biases:
+            self.bias[which] = self.ops.keep(tensors[n[which] + n["bias"]].float().contiguous())
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size() + \
+            4 * sum(b.numel() for b in self.bias.values() if b is not None)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(kv_heads=self.n_kv, head_dim=self.d, window=self.window or None,
+                          value_dim=self.dv if self.dv != self.d else 0)
+
+    def cache_bytes_read(self, kv_len: int) -> int:
+        keys = min(kv_len, self.window) if self.window else kv_len
+        return keys * self.n_kv * (self.d + self.dv) * self.ops.element_size
+
+    def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
+        ops = self.ops
+        if writes_cache != self.own_kv:
+            raise ValueError("sink_window_attention: a layer with projections of its own writes its lane, one without reads "
+                             "another's (the schedule and the layer disagree)")
+        if lane.k is not None:
+            ops.set_page_limit(lane.k.shape[0])
+        rot = self.position.rotary()
+        if rot is None or rot[1] != 1.0:
+            raise ValueError("sink_window_attention takes a rotation of pairs without a magnitude factor, or no position encoding")
+        inv_freq, _, rot_dim = rot
+        proj = ops.linear(y, self.w_in, out_f32=True)
+        q = ops.qk_prepare_store(ctx, proj, lane, self.n_heads, self.n_kv, self.d, self.dv,
+                                 (self.bias["q"], self.bias["k"], self.bias["v"]), inv_freq if rot_dim else None, rot_dim,
+                                 self.unit_rms, self.eps, has_kv=self.own_kv)
+        out = ops.sink_attention(ctx, q, lane, self.n_kv, self.dv, self.scale, self.window, self.softcap, self.sink)
+        return ops.linear(out, self.w_o)

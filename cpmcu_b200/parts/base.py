@@ -172,6 +172,14 @@ class CacheNeeds:
     def group_key(self) -> Tuple:
         return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values, self.value_dim)
 
+    def seen_through(self, window: Optional[int]) -> "CacheNeeds":
+        """The same needs when a further reader looks at the lane through ``window`` (None: at every key): the lane keeps
+        what its widest reader sees."""
+        if self.window is None or (window is not None and window <= self.window):
+            return self
+        return CacheNeeds(self.kv_heads, self.head_dim, window, self.pooled_stride, self.pooled_kernel, self.state, self.values,
+                          self.value_dim)
+
     def with_state(self, more: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]) -> "CacheNeeds":
         """The same needs with further per-sequence tensors (a block adds its own to its mixer's)."""
         both = dict(self.state)

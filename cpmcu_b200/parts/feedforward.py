@@ -76,6 +76,10 @@ class RoutedExperts(FeedForward):
         out = sum over the chosen e of s_e * down_e( act(gate_e y) * up_e y )            (s_e not renormalised)
             + sigmoid(w_sg . y) * shared(y)                                              (when ``shared_size`` > 0)
 
+    ``scoring`` "top_first" is another rule: the choice scores are the router's logits plus a bias
+    (``names["router_bias"]``, [experts]; ``router_bias`` False: none), the ``top`` largest are chosen, and the weights are
+    the softmax over the chosen logits only; it has no correction tensor and no groups.
+
     Expert e's matrices are ``<names["expert"]><e>.gate`` / ``.up`` / ``.down``; the shared expert's lie under
     ``names["shared"]`` with its gate vector ``names["shared_gate"]`` [1, hidden].  The router's product (with the
     shared gate's row appended) has 32-bit results; the experts' products run over the (token, expert) pairs grouped
@@ -84,11 +88,18 @@ class RoutedExperts(FeedForward):
 
     recordable_prompt = True
     DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e", "gate": ".gate", "up": ".up", "down": ".down",
-                     "shared": "shared.", "shared_gate": "shared.sg"}
+                     "shared": "shared.", "shared_gate": "shared.sg", "router_bias": "router.b"}
+    SCORINGS = ("softmax_first", "top_first")
 
     def __init__(self, ops, hidden_size: int, n_experts: int, top: int, expert_size: int, n_groups: int = 1, keep_groups: int = 1,
-                 shared_size: int = 0, names=None):
+                 shared_size: int = 0, names=None, scoring: str = "softmax_first", router_bias: bool = True):
         super().__init__(ops)
+        if scoring not in self.SCORINGS:
+            raise ValueError(f"routed_experts: scoring '{scoring}' is not built; known: {list(self.SCORINGS)}")
+        self.top_first = scoring == "top_first"
+        self.has_router_bias = self.top_first and bool(router_bias)
+        if self.top_first and int(n_groups) != 1:
+            raise ValueError("routed_experts: the rule that chooses first has no groups of experts")
         self.hidden_size, self.E, self.top, self.ff = int(hidden_size), int(n_experts), int(top), int(expert_size)
         self.n_groups, self.keep = int(n_groups), int(keep_groups)
         if self.E % self.n_groups or not 1 <= self.keep <= self.n_groups:
@@ -108,7 +119,11 @@ class RoutedExperts(FeedForward):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n, W, ff = self.names, self.hidden_size, self.ff
-        out = {n["router"]: WeightSpec((self.E, W)), n["correction"]: WeightSpec((self.E,), "vector")}
+        out = {n["router"]: WeightSpec((self.E, W))}
+        if not self.top_first:
+            out[n["correction"]] = WeightSpec((self.E,), "vector")
+        if self.has_router_bias:
+            out[n["router_bias"]] = WeightSpec((self.E,), "vector")
         for e in range(self.E):
             out[self._expert(e, "gate")] = WeightSpec((ff, W))
             out[self._expert(e, "up")] = WeightSpec((ff, W))
@@ -123,7 +138,8 @@ class RoutedExperts(FeedForward):
         n = self.names
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared is not None else [])
         self.w_router = self.ops.keep(torch.cat(rows, dim=0).contiguous())
-        self.correction = self.ops.keep(tensors[n["correction"]].float().contiguous())
+        self.correction = self.ops.keep(tensors[n["correction"]].float().contiguous()) if not self.top_first else None
+        self.router_bias = self.ops.keep(tensors[n["router_bias"]].float().contiguous()) if self.has_router_bias else None
         self.w_gate = self.ops.keep(torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)]).contiguous())
         self.w_up = self.ops.keep(torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous())
         self.w_down = self.ops.keep(torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous())
@@ -140,7 +156,8 @@ class RoutedExperts(FeedForward):
         ops = self.ops
         logits = ops.linear(y, self.w_router, out_f32=True)
         chosen, weights, gate = ops.moe_route(logits, self.correction, self.E, self.top, self.n_groups, self.keep,
-                                              gate_col=self.E if self.shared is not None else -1)
+                                              gate_col=self.E if self.shared is not None else -1, bias=self.router_bias,
+                                              top_first=self.top_first)
         taps = ctx.extras.get("taps")
         if taps is not None and not ctx.captured and taps.get("experts") is not None:
             taps["experts"].append(chosen.clone())          # a caller that wants to see the choice (tests do)

@@ -147,3 +147,62 @@ class GatedDeltaRule(_MatrixStateMixer):
                                                 b_col, b_col + H, H, G, d, dv, self.UNIT_EPS)
         o = ops.linear_recurrence(ctx, q, k, v, decay, beta, lane.state["matrix_state"], H, G, d, dv, d ** -0.5)
         return ops.linear(ops.gated_head_norm(o, proj[:, C:C + H * dv], self.w_norm, self.eps), self.w_o)
+
+
+@MIXERS.register("lightning_attention")
+class LightningAttention(_MatrixStateMixer):
+    """Linear attention with one fixed decay per head:
+
+        q = silu(Wq h),  k = silu(Wk h)   (heads x d),   v = silu(Wv h)   (heads x dv)
+        S_t = decay_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t * q_scale
+        out = Wo ( rms_norm(o) * w_norm * gate(Wg h) )
+
+    ``norm_heads``: how many heads the norm takes together ("all": the token's heads as one vector with a weight of
+    heads * dv numbers; 1: every head alone with a weight of dv numbers).  ``gate``: "sigmoid" or "silu".  The state
+    [heads, d, dv] is 32-bit per sequence; activations, decay, recurrence, norm and gate are 32-bit.
+    ``names``: "q", "k", "v", "g", "o", "norm".
+    """
+
+    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
+
+    def __init__(self, ops, hidden_size: int, n_heads: int, head_dim: int, value_dim: int, decay, eps: float,
+                 q_scale: float = 1.0, norm_heads="all", gate: str = "sigmoid", names=None):
+        super().__init__(ops)
+        self.hidden_size, self.heads, self.d, self.dv = int(hidden_size), int(n_heads), int(head_dim), int(value_dim)
+        self.decay_values = [float(a) for a in decay]
+        if len(self.decay_values) != self.heads:
+            raise ValueError(f"lightning_attention: {self.heads} heads need {self.heads} decays, got {len(self.decay_values)}")
+        self.eps, self.q_scale, self.gate = float(eps), float(q_scale), str(gate)
+        self.group = self.heads if norm_heads == "all" else int(norm_heads)
+        if self.heads % self.group:
+            raise ValueError(f"lightning_attention: {self.heads} heads cannot be normed in groups of {self.group}")
+        self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=ops.device) if ops is not None else None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W, H, d, dv = self.names, self.hidden_size, self.heads, self.d, self.dv
+        return {n["q"]: WeightSpec((H * d, W)), n["k"]: WeightSpec((H * d, W)), n["v"]: WeightSpec((H * dv, W)),
+                n["g"]: WeightSpec((H * dv, W)), n["o"]: WeightSpec((W, H * dv)), n["norm"]: WeightSpec((self.group * dv,), "vector")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in = self.ops.keep(torch.cat([tensors[n[x]] for x in ("q", "k", "v", "g")], dim=0).contiguous())
+        self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
+        self.w_norm = self._keep32(tensors[n["norm"]])
+        self.decay = self.ops.keep(torch.tensor(self.decay_values, dtype=torch.float32, device=self.w_norm.device))
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_norm))
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(state={"matrix_state": ((self.heads, self.d, self.dv), torch.float32)})
+
+    def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
+        ops, H, d, dv = self.ops, self.heads, self.d, self.dv
+        proj = ops.linear(y, self.w_in, out_f32=True)                       # [q | k | v | g]
+        ops.silu_columns(proj, 2 * H * d + H * dv)
+        q, k = proj[:, :H * d], proj[:, H * d:2 * H * d]
+        v, g = proj[:, 2 * H * d:2 * H * d + H * dv], proj[:, 2 * H * d + H * dv:]
+        decay = self.decay.unsqueeze(0).expand(ctx.n_tokens, H)             # the same row for every token (stride 0)
+        o = ops.linear_recurrence(ctx, q, k, v, decay, None, lane.state["matrix_state"], H, H, d, dv, self.q_scale)
+        return ops.linear(ops.gated_group_norm(o, g, self.w_norm, self.eps, self.group, self.gate), self.w_o)

@@ -16,17 +16,19 @@ from .base import NORMS, Norm, WeightSpec
 class RMSNorm(Norm):
     recordable_prompt = True
 
-    def __init__(self, ops, hidden_size: int, eps: float):
+    def __init__(self, ops, hidden_size: int, eps: float, weight_name: str = "weight"):
+        """``weight_name``: the tensor's name below the part's prefix."""
         super().__init__(ops)
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
+        self.weight_name = str(weight_name)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.hidden_size,), "vector")}
+        return {self.weight_name: WeightSpec((self.hidden_size,), "vector")}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = self.ops.keep(tensors["weight"].contiguous())
+        self.weight = self.ops.keep(tensors[self.weight_name].contiguous())
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

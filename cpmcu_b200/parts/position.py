@@ -60,6 +60,22 @@ class Rotary(PositionEncoding):
         return (self.inv_freq, self.magnitude, self.rot_dim)
 
 
+@POSITIONS.register("scaled_rope")
+class LinearlyScaledRotary(Rotary):
+    """A rotation of the first ``rot_dim`` channels of a head whose frequencies are all divided by one ``factor``
+    (positions stretched by it): inv_freq[i] = theta^(-2i/rot_dim) / factor.  The table is formed in 64-bit on the
+    host and rounded once to 32-bit; angles are 32-bit on the device."""
+
+    def __init__(self, ops, head_dim: int, theta: float, rot_dim: Optional[int] = None, factor: float = 1.0):
+        super().__init__(ops, head_dim, theta, rot_dim)
+        if not factor > 0:
+            raise ValueError(f"scaled_rope: the scaling factor must be positive, got {factor}")
+        self.factor = float(factor)
+        i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+        table = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / max(self.rot_dim, 1)) / self.factor
+        self.inv_freq = table.to(torch.float32).to(self.ops.device if self.ops is not None else "cpu")
+
+
 @POSITIONS.register("longrope")
 class LongRotary(Rotary):
     def __init__(self, ops, head_dim: int, theta: float, long_factor: Sequence[float],

@@ -113,6 +113,10 @@ def _register_builtin() -> None:
 
     register_architecture(Architecture(name=MufevikConfig.architecture, config_class=MufevikConfig, model_spec=mufevik.model_spec,
                                        fit_config=mufevik.fit_config_to_checkpoint))
+    from .config.kipizen import KipizenConfig
+    from .models import kipizen
+
+    register_architecture(Architecture(name=KipizenConfig.architecture, config_class=KipizenConfig, model_spec=kipizen.model_spec))
 
 
 _register_builtin()
