@@ -57,26 +57,40 @@ def sink_softmax(s: torch.Tensor, visible: torch.Tensor) -> torch.Tensor:
     return e / (torch.exp(-m) + e.sum(-1, keepdim=True))
 
 
+def window_attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap: float,
+                          window: Optional[int], sink: bool = True) -> torch.Tensor:
+    """q [T, H, d], k [T, G, d], v [T, G, dv] of one whole sequence -> [T, H, dv]: scores times ``scale``, capped by
+    cap * tanh(s / cap) (``cap`` 0: not capped), key j visible to query i when 0 <= i - j < window (None: j <= i),
+    softmax with a sink (or plain)."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    visible = (j <= i) if window is None else (j <= i) & (i - j < window)
+    out = []
+    for g in range(H):
+        s = (q[:, g] @ k[:, g // (H // G)].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        if sink:
+            pr = sink_softmax(s, visible)
+        else:
+            pr = torch.softmax(s.masked_fill(~visible, float("-inf")), dim=-1)
+        out.append(pr @ v[:, g // (H // G)])
+    return torch.stack(out, dim=1)
+
+
 def window_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, kv=None) -> torch.Tensor:
     """Grouped-query attention with biased projections, a rotation of part of each head, unit-rms queries and keys,
     capped scores, a sliding window and a sink.  ``kv``: another layer's (keys, values) used instead of own ones."""
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, d, dv = m["heads"], m["dim"], m["vdim"]
     q = (h @ w[p + "q"].T + w[p + "q.b"]).view(T, H, d)
     rot = m.get("rot") or {}
     q = rotate_half(q, rot.get("dims", 0), rot.get("base", 1.0), (rot.get("scaling") or {}).get("factor", 1.0))
     q = rms_norm(q, None, eps)
     k, v = kv if kv is not None else attention_keys_values(h, w, p, m, eps)
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
-    visible = (j <= i) & (i - j < m["mask"]["size"])
-    cap = m["softcap"]
-    out = []
-    for g in range(H):
-        s = (q[:, g] @ k[:, g // (H // G)].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
-        out.append(sink_softmax(s, visible) @ v[:, g // (H // G)])
-    return torch.stack(out, dim=1).reshape(T, H * dv) @ w[p + "o"].T
+    o = window_attention_core(q, k, v, m["scale"], m.get("softcap", 0.0), (m.get("mask") or {}).get("size"))
+    return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
 def lightning_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
@@ -113,13 +127,19 @@ def expert(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, chosen: Optional[torch.Tensor] = None):
+def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, chosen: Optional[torch.Tensor] = None,
+                       slack: Optional[list] = None):
     """Returns (output, logits, chosen).  ``chosen`` [T, top]: use these experts instead of the rule's (their weights
-    are still the softmax over their own logits)."""
+    are still the softmax over their own logits); ``slack`` then receives, per token, how far the lowest chosen logit
+    lies below the rule's cut-off (0 when the choice is the rule's)."""
     z, idx, wt = route(h, w, p, m)
     if chosen is not None:
+        cut = torch.gather(z, 1, idx).min(-1).values
         idx = chosen.long()
-        wt = torch.softmax(torch.gather(z, 1, idx), dim=-1)
+        picked = torch.gather(z, 1, idx)
+        if slack is not None:
+            slack.extend((cut - picked.min(-1).values).clamp_min(0).tolist())
+        wt = torch.softmax(picked, dim=-1)
     out = torch.zeros_like(h)
     for e in range(m["router"]["experts"]):
         hit = idx == e
@@ -129,9 +149,11 @@ def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: d
     return out, z, idx
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen: Optional[List[torch.Tensor]] = None, taps: Optional[dict] = None):
-    """Logits [T, vocab] of a whole sequence.  ``chosen``: per layer with a feed-forward, the experts to use.
-    ``taps``: receives "streams" (x after every layer), "logits" and "chosen" of the routers."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen: Optional[List[torch.Tensor]] = None, taps: Optional[dict] = None,
+            slack: Optional[list] = None):
+    """Logits [T, vocab] of a whole sequence.  ``chosen``: per layer with a feed-forward, the experts to use (``slack``:
+    see ``mixture_of_experts``).  ``taps``: receives "streams" (x after every layer), "logits" and "chosen" of the routers."""
+    w = {k: v.to(DT) if v.is_floating_point() else v for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
     kept = {}
@@ -151,7 +173,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen: Optional[List
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
             h2 = rms_norm(x, w[p + "norm2"], eps)
-            f, z, idx = mixture_of_experts(h2, w, p + "mlp.", layer["mlp"], None if chosen is None else chosen[n_ff])
+            f, z, idx = mixture_of_experts(h2, w, p + "mlp.", layer["mlp"], None if chosen is None else chosen[n_ff], slack)
             n_ff += 1
             if taps is not None:
                 taps.setdefault("logits", []).append(z)
@@ -160,3 +182,14 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen: Optional[List
         if taps is not None:
             taps.setdefault("streams", []).append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt, n_new: int):
+    """(the n_new tokens greedy decoding appends, the gap between the two best logits at every choice)."""
+    ids, out, gaps = list(prompt), [], []
+    for _ in range(n_new):
+        top = torch.topk(forward(cfg, w, ids)[-1], 2)
+        out.append(int(top.indices[0]))
+        gaps.append(float(top.values[0] - top.values[1]))
+        ids.append(out[-1])
+    return out, gaps
