@@ -17,27 +17,7 @@
 // Softmax statistics, scores and output accumulators are fp32; probabilities are rounded
 // to bf16 for the second product, as in the reference (src/flash_attn/src/flash_fwd_kernel.h:1560-1616).
 #include "common.cuh"
-
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Keys and values are read once by one warp: keep them out of L1.
-__device__ __forceinline__ uint4 ldg16(const void* p) {
-    uint4 v;
-    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
+#include "mma_bf16.cuh"
 
 // State of a 16-row tile in one warp: thread (g = lane / 4, j = lane % 4) holds rows g and
 // g + 8; o[nt] are output dims 8*nt + 2j, 2j+1 of both rows.

@@ -8,6 +8,7 @@
 // Query and key heads have d channels, value heads dv.  Everything between the projections and the weighted sum of
 // values is fp32: biases, angles, the rotation, the unit root mean square of q and k, scores, cap, weights.
 #include "common.cuh"
+#include "mma_bf16.cuh"
 
 constexpr int kPrepMaxPerLane = 8;      // heads of up to 256 channels
 constexpr int kPrepWarps = 4;
@@ -202,6 +203,335 @@ CPM_API int cpm_sink_attention_generic(const void* q, const void* k_cache, const
                    (const float*)k_cache, (const float*)v_cache, (float*)out, positions, token_seq, slots, page_table, max_pages,
                    window, n_heads, n_kv, d, dv, scale, cap, sink);
     return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// bf16 on the tensor cores.  A warp owns 16 rows (query tokens of one head in a prompt; the query heads that share a
+// key-value head for a single token) and walks over the keys its rows can see, 32 at a time, straight from the pages
+// (16-byte loads along the head size for the scores and along the token axis of the transposed value pages for the
+// weighted sum; the thread-to-key assignment is the one of attention_bf16.cu).  Scores, cap, running maximum and sum
+// are fp32.  The weights enter the second product as two bf16 numbers each (the rounded weight and what the rounding
+// left over), so that they carry 16 bits of mantissa into the fp32 accumulators instead of 8.  The sink joins when a
+// row is finished: one more term exp(0 - max) in the sum.
+// ---------------------------------------------------------------------------
+template <int DV>
+struct SinkTile {
+    float o[DV / 8][4];
+    float m[2];      // running maximum, log2 domain
+    float l[2];      // this thread's share of the running sum
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+    }
+};
+
+// tanh from one exponential: 1 - 2 / (e^(2x) + 1); exact limits at both ends (e = 0 and e = inf)
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
+__device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = pack_bf16(a - __low2float(h), b - __high2float(h));
+}
+
+// 32 keys key0 .. key0 + 31 of one page (khalf: their rows of the key page; vhalf: value page + their token offset).
+// Row r sees key when lo[r] <= key <= hi[r].
+template <int D, int DV>
+__device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (&q)[2][D / 32], const bf16* __restrict__ khalf,
+                                                 const bf16* __restrict__ vhalf, int key0, const int (&lo)[2],
+                                                 const int (&hi)[2], float scale, float cap, int lane) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int j = lane & 3, n = lane >> 2;
+    float s[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+        const bf16* kp = khalf + (8 * (n >> 1) + 2 * t + (n & 1)) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) {
+            const uint4 kv = ldg16(kp + 32 * w);
+            mma_16816(s[t], q[0][w].x, q[1][w].x, q[0][w].y, q[1][w].y, kv.x, kv.y);
+            mma_16816(s[t], q[0][w].z, q[1][w].z, q[0][w].w, q[1][w].w, kv.z, kv.w);
+        }
+    }
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f, cap_log2 = cap * kLog2e, scale_log2 = scale * kLog2e;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1, key = key0 + 8 * j + 2 * t + (e & 1);
+            float x = cap > 0.f ? cap_log2 * tanh_by_exp(s[t][e] * scale * inv_cap) : s[t][e] * scale_log2;
+            x = (key >= lo[r] && key <= hi[r]) ? x : -INFINITY;
+            s[t][e] = x;
+            mx[r] = fmaxf(mx[r], x);
+        }
+    float use[2], corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float mn = fmaxf(st.m[r], mx[r]);
+        use[r] = mn == -INFINITY ? 0.f : mn;
+        corr[r] = exp2f(st.m[r] - use[r]);
+        st.m[r] = mn;
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pr = exp2f(s[t][e] - use[e >> 1]);
+            s[t][e] = pr;
+            sum[e >> 1] += pr;
+        }
+    st.l[0] = st.l[0] * corr[0] + sum[0];
+    st.l[1] = st.l[1] * corr[1] + sum[1];
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+        st.o[nt][0] *= corr[0];
+        st.o[nt][1] *= corr[0];
+        st.o[nt][2] *= corr[1];
+        st.o[nt][3] *= corr[1];
+    }
+    uint32_t ah[4], al[4], ch[4], cl[4];
+    split_bf16(s[0][0], s[0][1], ah[0], al[0]);
+    split_bf16(s[0][2], s[0][3], ah[1], al[1]);
+    split_bf16(s[1][0], s[1][1], ah[2], al[2]);
+    split_bf16(s[1][2], s[1][3], ah[3], al[3]);
+    split_bf16(s[2][0], s[2][1], ch[0], cl[0]);
+    split_bf16(s[2][2], s[2][3], ch[1], cl[1]);
+    split_bf16(s[3][0], s[3][1], ch[2], cl[2]);
+    split_bf16(s[3][2], s[3][3], ch[3], cl[3]);
+    const bf16* vp = vhalf + n * kPageTokens + 8 * j;
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+        const uint4 vv = ldg16(vp + nt * 8 * kPageTokens);
+        mma_16816(st.o[nt], ah[0], ah[1], ah[2], ah[3], vv.x, vv.y);
+        mma_16816(st.o[nt], ch[0], ch[1], ch[2], ch[3], vv.z, vv.w);
+        mma_16816(st.o[nt], al[0], al[1], al[2], al[3], vv.x, vv.y);
+        mma_16816(st.o[nt], cl[0], cl[1], cl[2], cl[3], vv.z, vv.w);
+    }
+}
+
+// Finishes a tile: the quad's shares of the sums join, the sink adds exp(0 - max), and rows [0, n_rows) go out as bf16.
+// out_row(r) gives the output row (dv channels) of tile row g + 8r.
+template <int DV, typename RowFn>
+__device__ __forceinline__ void sink_finish(SinkTile<DV>& st, int sink, int lane, RowFn out_row) {
+    const int j = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (sink) l += st.m[r] == -INFINITY ? 1.f : exp2f(-st.m[r]);
+        bf16* orow = out_row(r);
+        if (orow == nullptr) continue;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * j) = pack_bf16(st.o[nt][2 * r] * inv, st.o[nt][2 * r + 1] * inv);
+    }
+}
+
+// Prompt tokens: a block of 4 warps takes 64 consecutive query tokens of one sequence and one head, 16 a warp (the
+// tile lists of the plain prefill kernel).  A warp walks from the first key its first token sees to its last token.
+constexpr int kSinkTileWarps = 4;
+
+template <int D, int DV>
+__global__ void __launch_bounds__(kSinkTileWarps * 32)
+sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                            bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
+                            const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
+                            const int* __restrict__ page_table, int max_pages, int window, int n_heads, int n_kv, float scale,
+                            float cap, int sink) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = lane & 3, g = lane >> 2;
+    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int seq = tile_seq[tile], h = blockIdx.x;
+    const int kvh = h / (n_heads / n_kv);
+    const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+    const int row0 = tile_row[tile] + 16 * warp;
+    if (row0 >= q_len) return;
+    const int history = kv_len[seq] - q_len;
+    const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+    uint4 qf[2][D / 32];
+    int lo[2], hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + g + 8 * r;
+        const bool valid = row < q_len;
+        hi[r] = valid ? history + row : -1;
+        lo[r] = (valid && window > 0) ? max(0, hi[r] - window + 1) : 0;
+        const bf16* qrow = q + ((int64_t)(q_begin + (valid ? row : row0)) * n_heads + h) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+    }
+    SinkTile<DV> st;
+    st.init();
+    const int first = window > 0 ? max(0, history + row0 - window + 1) : 0;
+    const int last = history + min(row0 + 16, q_len) - 1;
+    for (int key0 = first & ~31; key0 <= last; key0 += 32) {
+        const int page = CPM_PAGE(pages, key0 / kPageTokens, max_pages), off = key0 % kPageTokens;
+        sink_attend_keys<D, DV>(st, qf, k_cache + page_row_offset(page, kvh, off, n_kv, D),
+                                v_cache + value_offset(page, kvh, 0, off, n_kv, DV), key0, lo, hi, scale, cap, lane);
+    }
+    sink_finish<DV>(st, sink, lane, [&](int r) -> bf16* {
+        const int row = row0 + g + 8 * r;
+        return row < q_len ? out + ((int64_t)(q_begin + row) * n_heads + h) * DV : nullptr;
+    });
+}
+
+// Single tokens (a decode step; also any step without tile lists): a block takes one token, one key-value head and up
+// to 16 of the query heads that share it as the rows of a tile; its warps split the token's keys among them, 32 at a
+// time, and join their maxima, sums and outputs through shared memory.
+constexpr int kSinkTokenWarps = 4;
+
+template <int D, int DV>
+__global__ void __launch_bounds__(kSinkTokenWarps * 32)
+sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                            bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                            const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages, int window,
+                            int n_heads, int n_kv, float scale, float cap, int sink) {
+    __shared__ float part_o[kSinkTokenWarps - 1][16][DV + 1];
+    __shared__ float part_ml[kSinkTokenWarps - 1][16][2];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = lane & 3, g = lane >> 2;
+    const int t = blockIdx.x;
+    const int group = n_heads / n_kv, chunks = (group + 15) / 16;
+    const int kvh = blockIdx.y / chunks, h0 = kvh * group + (blockIdx.y % chunks) * 16;
+    const int rows = min(16, (kvh + 1) * group - h0);
+    const int p = positions[t];
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    uint4 qf[2][D / 32];
+    int lo[2], hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        const bool valid = row < rows;
+        hi[r] = valid ? p : -1;
+        lo[r] = (valid && window > 0) ? max(0, p - window + 1) : 0;
+        const bf16* qrow = q + ((int64_t)t * n_heads + h0 + (valid ? row : 0)) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+    }
+    SinkTile<DV> st;
+    st.init();
+    const int first = (window > 0 ? max(0, p - window + 1) : 0) & ~31;
+    const int n_blocks = (p - first) / 32 + 1;
+    const int share = (n_blocks + kSinkTokenWarps - 1) / kSinkTokenWarps;
+    const int b_end = min(n_blocks, (warp + 1) * share);
+    for (int b = warp * share; b < b_end; ++b) {
+        const int key0 = first + 32 * b;
+        const int page = CPM_PAGE(pages, key0 / kPageTokens, max_pages), off = key0 % kPageTokens;
+        sink_attend_keys<D, DV>(st, qf, k_cache + page_row_offset(page, kvh, off, n_kv, D),
+                                v_cache + value_offset(page, kvh, 0, off, n_kv, DV), key0, lo, hi, scale, cap, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+    if (warp > 0) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
+            if (j == 0) {
+                part_ml[warp - 1][row][0] = st.m[r];
+                part_ml[warp - 1][row][1] = st.l[r];
+            }
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                part_o[warp - 1][row][8 * nt + 2 * j] = st.o[nt][2 * r];
+                part_o[warp - 1][row][8 * nt + 2 * j + 1] = st.o[nt][2 * r + 1];
+            }
+        }
+    }
+    __syncthreads();
+    if (warp > 0) return;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        float m = st.m[r];
+#pragma unroll
+        for (int w = 0; w < kSinkTokenWarps - 1; ++w) m = fmaxf(m, part_ml[w][row][0]);
+        const float use = m == -INFINITY ? 0.f : m;
+        const float mine = exp2f(st.m[r] - use);
+        float l = st.l[r] * mine;
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            st.o[nt][2 * r] *= mine;
+            st.o[nt][2 * r + 1] *= mine;
+        }
+#pragma unroll
+        for (int w = 0; w < kSinkTokenWarps - 1; ++w) {
+            const float f = exp2f(part_ml[w][row][0] - use);
+            l += part_ml[w][row][1] * f;
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                st.o[nt][2 * r] = fmaf(part_o[w][row][8 * nt + 2 * j], f, st.o[nt][2 * r]);
+                st.o[nt][2 * r + 1] = fmaf(part_o[w][row][8 * nt + 2 * j + 1], f, st.o[nt][2 * r + 1]);
+            }
+        }
+        if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
+        if (row >= rows) continue;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* orow = out + ((int64_t)t * n_heads + h0 + row) * DV + 2 * j;
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + 8 * nt) = pack_bf16(st.o[nt][2 * r] * inv, st.o[nt][2 * r + 1] * inv);
+    }
+}
+
+template <int D, int DV>
+static int launch_sink_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
+                            const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* positions,
+                            const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
+                            int n_tokens, int n_heads, int n_kv, float scale, float cap, int sink, cudaStream_t stream) {
+    if (n_tiles > 0) {
+        cpm_launch(kLaunchAttention, sink_attention_tiles_kernel<D, DV>, dim3(n_heads, n_tiles), dim3(kSinkTileWarps * 32), 0,
+                   stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q,
+                   kv_len, slots, page_table, max_pages, window, n_heads, n_kv, scale, cap, sink);
+    } else {
+        const int group = n_heads / n_kv;
+        cpm_launch(kLaunchAttention, sink_attention_token_kernel<D, DV>, dim3(n_tokens, n_kv * ((group + 15) / 16)),
+                   dim3(kSinkTokenWarps * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                   (bf16*)out, positions, token_seq, slots, page_table, max_pages, window, n_heads, n_kv, scale, cap, sink);
+    }
+    return launch_status();
+}
+
+// Whether the tensor-core kernels are built for these head sizes.
+CPM_API int cpm_sink_attention_bf16_sizes(int d, int dv) {
+    return (d == 32 || d == 64 || d == 96 || d == 128) && (dv == 32 || dv == 64 || dv == 96 || dv == 128);
+}
+
+// bf16 q [tokens, heads, d] -> out [tokens, heads * dv].  With n_tiles > 0 the tokens are prompt tokens packed by
+// sequence (cu_q, kv_len, tile lists of 64 rows); else every token is taken alone by its position and sequence.
+CPM_API int cpm_sink_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
+                                    const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len,
+                                    const int* positions, const int* token_seq, const int* slots, const int* page_table,
+                                    int max_pages, int window, int n_tokens, int n_heads, int n_kv, int d, int dv, float scale,
+                                    float cap, int sink, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (!cpm_sink_attention_bf16_sizes(d, dv) || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || n_tiles > 65535)
+        return CPM_BAD_ARGUMENT;
+    if (n_tiles > 0 ? (!tile_seq || !tile_row || !cu_q || !kv_len) : (!positions || !token_seq)) return CPM_BAD_ARGUMENT;
+#define CPM_SINK_CASE(DD, VV)                                                                                              \
+    if (d == DD && dv == VV)                                                                                               \
+        return launch_sink_bf16<DD, VV>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, positions,    \
+                                        token_seq, slots, page_table, max_pages, window, n_tokens, n_heads, n_kv, scale,   \
+                                        cap, sink, stream);
+#define CPM_SINK_ROW(DD) CPM_SINK_CASE(DD, 32) CPM_SINK_CASE(DD, 64) CPM_SINK_CASE(DD, 96) CPM_SINK_CASE(DD, 128)
+    CPM_SINK_ROW(32) CPM_SINK_ROW(64) CPM_SINK_ROW(96) CPM_SINK_ROW(128)
+#undef CPM_SINK_ROW
+#undef CPM_SINK_CASE
+    return CPM_BAD_ARGUMENT;
 }
 
 CPM_BOUNDS_TU(sink_attention)

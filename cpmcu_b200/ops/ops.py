@@ -919,8 +919,34 @@ class Ops:
                        sink: bool = True) -> torch.Tensor:
         """q [tokens, heads, d] over the lane's cached keys and values -> [tokens, heads*dv]: scores times ``scale``, capped
         by cap * tanh(s / cap) when ``cap`` > 0, keys 0 <= i - j < ``window`` (0: all before and at i), softmax with one
-        added to the denominator when ``sink``.  Picks the kernel."""
+        added to the denominator when ``sink``.  Picks the kernel: bf16 with head sizes the tensor-core kernels are built
+        for goes to them (prompt tokens by the step's query tiles, anything else token by token); other sizes and the
+        32-bit path go to the kernel of every size."""
+        n, n_heads, d = q.shape
+        if (self.code == BF16 and self.lib.cpm_sink_attention_bf16_sizes(d, dv)
+                and os.environ.get("CPMCU_SINK_GENERIC", "0") != "1"):
+            return self.sink_attention_bf16(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
         return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
+
+    SINK_TILE_MIN_ROWS = 8       # shorter portions than this go token by token (a tile of 16 rows would be mostly empty)
+
+    def sink_attention_bf16(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
+                            sink: bool) -> torch.Tensor:
+        """The tensor-core kernels (bf16 operands; scores, cap, maxima, sums and accumulators fp32; a weight enters the
+        product with the values as the sum of two bf16 numbers).  A warp owns 16 rows: query tokens of one head in a prompt
+        (``ctx.q_tiles``), the query heads of one key-value head for a token taken alone."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        out = self.empty(n, n_heads * dv)
+        tiles = None if ctx.is_decode or ctx.max_q_len < self.SINK_TILE_MIN_ROWS else ctx.q_tiles
+        tile_seq, tile_row, n_tiles = tiles if tiles is not None else (None, None, 0)
+        check(self.lib.cpm_sink_attention_bf16(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(tile_seq), _ptr(tile_row),
+                                               int(n_tiles), _ptr(ctx.cu_q), _ptr(ctx.kv_len_dev), _ptr(ctx.positions),
+                                               _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                               lane.page_table.shape[1], int(window), n, n_heads, n_kv, d, dv, float(scale),
+                                               float(cap), 1 if sink else 0, self._stream()),
+              f"sink attention on tensor cores ({n_heads} heads, {d} / {dv})")
+        return out
 
     def sink_attention_generic(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
                                sink: bool) -> torch.Tensor:

@@ -259,3 +259,298 @@ def test_command_line_and_replay(folders, tmp_path):
     assert not (out / "1.f32").exists()
     check(got0, want[[0, 16]], "float32", "replay")
     check(got2, want[[29]], "float32", "replay")
+
+
+# ---------------------------------------------------------------------------
+# mechanisms alone
+# ---------------------------------------------------------------------------
+
+def _ctx(q_lens, starts, slots):
+    """A step's description on the device for sequences that bring ``q_lens`` tokens from positions ``starts``."""
+    from cpmcu_b200.parts.base import QUERY_TILE_TOKENS, StepContext
+
+    i32 = dict(dtype=torch.int32, device="cuda")
+    pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), **i32)
+    kv = [s + n for n, s in zip(q_lens, starts)]
+    ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                      q_lens=list(q_lens), kv_lens=kv, slots=list(slots), max_q_len=max(q_lens), max_kv_len=max(kv),
+                      token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                      kv_len_dev=torch.tensor(kv, **i32), slot_dev=torch.tensor(list(slots), **i32))
+    ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+    trow = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+    ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(trow, **i32), len(ts))
+    return ctx
+
+
+def _close(got, want, dtype, tol32=3e-5, tol16=2e-2):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    assert err <= (tol32 if dtype == "float32" else tol16), err
+
+
+def _towers(T, window):
+    """(query, key) pairs whose score towers, and keys that tower but must stay unseen (later than the query, or the
+    first one a window has dropped)."""
+    seen, unseen = [], []
+    w = window or T + 1
+    for qi in (T - 1, T - 2, 150, 151, 130, 127, 128, 64, 63, 1):
+        seen.append((qi, qi - w + 1 if qi - w + 1 >= 0 else 0))                # the last key a window holds, or the first key
+        if qi - w >= 0:
+            unseen.append((qi, qi - w))                                       # the first key the window has dropped
+    seen += [(190, 190), (100, 63 if w > 37 else 100), (101, 64 if w > 37 else 101), (0, 0)]
+    return seen, unseen
+
+
+ATTENTION_SIZES = [
+    # H, G, d, dv, window, cap, sink
+    (6, 3, 128, 128, 70, 20.0, True), (8, 2, 64, 32, 64, 0.0, True), (4, 1, 32, 96, None, 7.0, True), (34, 2, 32, 32, 1, 0.0, True),
+    (3, 3, 96, 64, 33, 30.0, False), (5, 5, 12, 36, 129, 15.0, True), (4, 2, 24, 40, None, 0.0, True), (2, 1, 200, 130, 65, 50.0, True),
+    (16, 1, 64, 128, 200, 25.0, True), (2, 2, 128, 64, 2, 0.0, False),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("generic", [True, False])
+@pytest.mark.parametrize("H,G,d,dv,window,cap,sink", ATTENTION_SIZES)
+def test_sink_window_attention_sees_its_window_and_the_sink(dtype, generic, H, G, d, dv, window, cap, sink):
+    """Queries and keys enter as they are (no bias, rotation or norm), so only the scores, the cap, the window, the sink
+    and the weighted sum are under test.  A score towers at the last key a window still holds, at the first key, on
+    both sides of page borders and at the query itself; a larger one stands at the first key the window has dropped and
+    right after the query.  Some queries are zero: their weights are 1 / (keys + 1) with the sink and 1 / keys without.
+    One prompt; a prompt, then single tokens; portions of 70, 2, 61, 5 and single tokens; slots and pages that are not
+    the first; by the kernel of every size and by the library's choice (tensor cores where the sizes fit)."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    if not generic and not (dtype == "bfloat16" and d % 32 == 0 and dv % 32 == 0 and d <= 128 and dv <= 128):
+        pytest.skip("the library's choice is the kernel of every size")
+    ops = Ops(DT[dtype])
+    g = torch.Generator().manual_seed(H * d + dv)
+    T = 230
+    q = torch.randn(T, H, d, generator=g) * 0.5
+    k = torch.randn(T, G, d, generator=g) * 0.5
+    v = torch.randn(T, G, dv, generator=g)
+    spike = d - 1
+    seen, unseen = _towers(T, window)
+    for qi, kj in seen:
+        q[qi, :, spike] = 9.0
+        k[kj, :, spike] = 9.0
+    marked = {qi for qi, _ in seen} | {kj for _, kj in seen}
+    for qi, kj in unseen:
+        if kj not in marked:
+            k[kj, :, spike] = 30.0
+    for qi, _ in seen:
+        if qi + 1 < T and qi + 1 not in marked:
+            k[qi + 1, :, spike] = 30.0                                        # later than the query
+    q[110:114] = 0.0
+    scale = 0.3
+    rnd = lambda t: t.to(DT[dtype]).double()
+    want = plain.window_attention_core(rnd(q), rnd(k), rnd(v), scale, cap, window, sink).reshape(T, H * dv)
+    proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1).to(DT[dtype]).float().cuda()
+    needs = CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0, window=window)
+    fn = ops.sink_attention_generic if generic else ops.sink_attention
+    for pieces in ([T], [T - 40] + [1] * 40, [70, 2, 61, 5] + [1] * (T - 138)):
+        cache = Cache([needs], max_tokens=64 * 12, dtype=DT[dtype], device="cuda:0", n_slots=3)
+        cache.open_sequence()
+        other = cache.open_sequence()
+        cache.reserve(other, 130)
+        slot = cache.open_sequence()
+        lane = cache.lane(0)
+        outs, at = [], 0
+        for n in pieces:
+            cache.reserve(slot, at + n)
+            cache.sync()
+            ctx = _ctx([n], [at], [slot])
+            qr = ops.qk_prepare_store(ctx, proj[at:at + n].contiguous(), lane, H, G, d, dv, (None, None, None), None, 0, False, 0.0)
+            outs.append(fn(ctx, qr, lane, G, dv, scale, window or 0, cap, sink))
+            at += n
+        got = torch.cat(outs)
+        _close(got, want, dtype)
+        for qi in sorted({qi for qi, _ in seen} | {110, 113}):
+            _close(got[qi], want[qi], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sink_window_attention_batches_unequal_sequences(dtype):
+    """Three sequences of different lengths and histories in one step, prompt portions and then single tokens together,
+    against each sequence alone by the plain implementation."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = Ops(DT[dtype])
+    H, G, d, dv, window, cap, scale = 4, 2, 64, 64, 40, 12.0, 0.25
+    g = torch.Generator().manual_seed(5)
+    lens = [150, 9, 77]
+    data = [(torch.randn(n, H, d, generator=g), torch.randn(n, G, d, generator=g), torch.randn(n, G, dv, generator=g)) for n in lens]
+    rnd = lambda t: t.to(DT[dtype]).double()
+    want = [plain.window_attention_core(rnd(q), rnd(k), rnd(v), scale, cap, window).reshape(n, H * dv) for (q, k, v), n in zip(data, lens)]
+    cache = Cache([CacheNeeds(kv_heads=G, head_dim=d, window=window)], max_tokens=64 * 10, dtype=DT[dtype], device="cuda:0", n_slots=4)
+    cache.open_sequence()
+    slots = [cache.open_sequence() for _ in lens]
+    lane = cache.lane(0)
+    done = [0] * 3
+    got = [[] for _ in lens]
+    steps = [[100, 5, 70], [45, 3, 6]] + [[1, 1, 1]] * 5
+    for step in steps:
+        take = [min(s, n - a) for s, n, a in zip(step, lens, done)]
+        live = [i for i in range(3) if take[i] > 0]
+        for i in live:
+            cache.reserve(slots[i], done[i] + take[i])
+        cache.sync()
+        ctx = _ctx([take[i] for i in live], [done[i] for i in live], [slots[i] for i in live])
+        proj = torch.cat([torch.cat([t[done[i]:done[i] + take[i]].reshape(take[i], -1) for t in data[i]], dim=1) for i in live])
+        qr = ops.qk_prepare_store(ctx, proj.to(DT[dtype]).float().cuda().contiguous(), lane, H, G, d, dv, (None, None, None), None, 0,
+                                  False, 0.0)
+        o = ops.sink_attention(ctx, qr, lane, G, dv, scale, window, cap, True)
+        at = 0
+        for i in live:
+            got[i].append(o[at:at + take[i]])
+            at += take[i]
+            done[i] += take[i]
+    for i in range(3):
+        _close(torch.cat(got[i]), want[i][:done[i]], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,d,dv,rot_dim,base,factor", [(4, 2, 64, 64, 32, 20000.0, 2.0), (3, 1, 24, 40, 24, 300.0, 1.0),
+                                                            (2, 2, 128, 32, 0, 1.0, 1.0), (5, 5, 20, 20, 8, 1e6, 7.5)])
+def test_biases_rotation_and_unit_lengths_before_the_cache(dtype, H, G, d, dv, rot_dim, base, factor):
+    """The whole mixer with identity projections against the plain one: biases on q, k and v, the rotation of the first
+    channels of a head in pairs (i, i + dims/2) with stretched positions, unit root mean square per head, and a second
+    layer's queries over the first layer's cached keys and values."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+    from cpmcu_b200.parts.position import LinearlyScaledRotary
+
+    ops = Ops(DT[dtype])
+    g = torch.Generator().manual_seed(d + dv)
+    T, eps, scale, window, cap = 140, 1e-5, 0.9, 50, 10.0
+    q = torch.randn(T, H * d, generator=g)
+    k = torch.randn(T, G * d, generator=g)
+    v = torch.randn(T, G * dv, generator=g)
+    q2 = torch.randn(T, H * d, generator=g)
+    bq, bk, bv, bq2 = (torch.randn(n, generator=g) for n in (H * d, G * d, G * dv, H * d))
+    W = q.shape[1] + k.shape[1] + v.shape[1]
+    h = torch.cat([q, k, v], dim=1).double()
+    eye = torch.eye(W, dtype=torch.float64)
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "scale": scale, "softcap": cap, "mask": {"size": window}}
+    if rot_dim:
+        m["rot"] = {"dims": rot_dim, "base": base, "scaling": {"factor": factor}}
+    w = {"q": eye[:H * d], "k": eye[H * d:H * d + G * d], "v": eye[H * d + G * d:], "o": torch.eye(H * dv, dtype=torch.float64),
+         "q.b": bq.double(), "k.b": bk.double(), "v.b": bv.double()}
+    want = plain.window_attention(h, w, "", m, eps)
+    kv = plain.attention_keys_values(h, w, "", m, eps)
+    w2 = dict(w, **{"q": torch.eye(H * d, dtype=torch.float64), "q.b": bq2.double()})
+    want2 = plain.window_attention(q2.double(), w2, "", m, eps, kv=kv)
+    inv_freq = LinearlyScaledRotary(ops, d, base, rot_dim, factor).inv_freq if rot_dim else None
+    needs = CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0, window=window)
+    for pieces in ([T], [T - 20] + [1] * 20, [3, 66, 2] + [1] * (T - 71)):
+        cache = Cache([needs], max_tokens=64 * 8, dtype=DT[dtype], device="cuda:0", n_slots=2)
+        cache.open_sequence()
+        slot = cache.open_sequence()
+        lane = cache.lane(0)
+        outs, outs2, at = [], [], 0
+        for n in pieces:
+            cache.reserve(slot, at + n)
+            cache.sync()
+            ctx = _ctx([n], [at], [slot])
+            qr = ops.qk_prepare_store(ctx, h[at:at + n].float().cuda().contiguous(), lane, H, G, d, dv,
+                                      (bq.cuda(), bk.cuda(), bv.cuda()), inv_freq, rot_dim, True, eps)
+            outs.append(ops.sink_attention(ctx, qr, lane, G, dv, scale, window, cap, True))
+            qr2 = ops.qk_prepare_store(ctx, q2[at:at + n].float().cuda().contiguous(), lane, H, G, d, dv, (bq2.cuda(), None, None),
+                                       inv_freq, rot_dim, True, eps, has_kv=False)
+            outs2.append(ops.sink_attention(ctx, qr2, lane, G, dv, scale, window, cap, True))
+            at += n
+        _close(torch.cat(outs), want, dtype, tol32=5e-5, tol16=3e-2)
+        _close(torch.cat(outs2), want2, dtype, tol32=5e-5, tol16=3e-2)
+
+
+@pytest.mark.parametrize("H,d,dv", [(3, 20, 24), (6, 32, 64), (1, 72, 16), (2, 128, 130), (5, 8, 8)])
+def test_lightning_recurrence_in_one_piece_and_in_pieces(H, d, dv):
+    """One decay per head (one of them 1, one small), three sequences at once in slots that hold rubbish, in one piece,
+    in two and in pieces down to single tokens; the state lives on between the steps."""
+    from cpmcu_b200.ops.ops import Ops
+
+    ops = Ops(torch.float32)
+    g = torch.Generator().manual_seed(d * dv + H)
+    decay = torch.rand(H, generator=g) * 0.5 + 0.5
+    decay[0] = 1.0
+    decay[-1] = 0.05 if H > 1 else 0.9
+    lens = [90, 1, 37]
+    ins, want = [], []
+    for n in lens:
+        q, k, v = torch.rand(n, H, d, generator=g), torch.rand(n, H, d, generator=g) - 0.3, torch.randn(n, H, dv, generator=g)
+        ins.append((q, k, v))
+        want.append(plain.lightning_recurrence(q.double(), k.double(), v.double(), decay.double())[0])
+    for cuts in ([1.0], [0.5, 1.0], [0.1, 0.2, 0.6, 1.0], [i / 45 for i in range(1, 46)]):
+        state = torch.full((5, H, d, dv), 7.0, device="cuda")
+        slots = [4, 0, 2]
+        got = [[] for _ in lens]
+        done = [0] * len(lens)
+        for c in cuts:
+            upto = [max(done[i] + 1, int(round(n * c))) if done[i] < n else n for i, n in enumerate(lens)]
+            upto = [min(u, n) for u, n in zip(upto, lens)]
+            live = [i for i in range(len(lens)) if upto[i] > done[i]]
+            if not live:
+                continue
+            ctx = _ctx([upto[i] - done[i] for i in live], [done[i] for i in live], [slots[i] for i in live])
+            cat = lambda j: torch.cat([ins[i][j][done[i]:upto[i]].reshape(upto[i] - done[i], -1) for i in live]).cuda().contiguous()
+            dec = decay.cuda().unsqueeze(0).expand(ctx.n_tokens, H)
+            o = ops.linear_recurrence(ctx, cat(0), cat(1), cat(2), dec, None, state, H, H, d, dv, 1.0)
+            at = 0
+            for i in live:
+                got[i].append(o[at:at + upto[i] - done[i]])
+                at += upto[i] - done[i]
+                done[i] = upto[i]
+        for i in range(len(lens)):
+            _close(torch.cat(got[i]), want[i], "float32")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,dv,group,act", [(6, 64, 6, "sigmoid"), (3, 24, 3, "sigmoid"), (4, 16, 2, "silu"), (1, 130, 1, "sigmoid"), (5, 8, 1, "silu")])
+def test_norm_over_heads_with_gate_and_activations_in_place(dtype, H, dv, group, act):
+    from cpmcu_b200.ops.ops import Ops
+
+    ops = Ops(DT[dtype])
+    g = torch.Generator().manual_seed(H * dv)
+    T, eps = 37, 1e-5
+    o = torch.randn(T, H, dv, generator=g) * 3
+    row = torch.randn(T, H * dv + 5, generator=g)                      # the gate is a slice of a wider row
+    weight = torch.randn(group * dv, generator=g)
+    x = o.double().view(T, H // group, group * dv)
+    want = plain.rms_norm(x, weight.double(), eps).reshape(T, H * dv)
+    gate = row[:, 5:].double()
+    want = want * (torch.sigmoid(gate) if act == "sigmoid" else plain.silu(gate))
+    got = ops.gated_group_norm(o.cuda(), row.cuda()[:, 5:], weight.cuda(), eps, group, act)
+    _close(got, want, dtype)
+    wide = torch.randn(T, 50, generator=g)
+    got = ops.silu_columns(wide.clone().cuda(), 33)
+    _close(got[:, :33], plain.silu(wide[:, :33].double()), "float32")
+    assert torch.equal(got[:, 33:].cpu(), wide[:, 33:])
+
+
+@pytest.mark.parametrize("E,top", [(8, 4), (10, 3), (6, 6), (5, 1), (64, 6), (300, 8)])
+def test_routing_by_logit_with_bias_and_softmax_over_the_chosen(E, top):
+    from cpmcu_b200.ops.ops import Ops
+
+    ops = Ops(torch.float32)
+    g = torch.Generator().manual_seed(E + top)
+    T = 50
+    z = torch.randn(T, E + 3, generator=g) * 3                           # rows wider than the experts
+    z[7] = -40.0 - torch.arange(E + 3)                                   # all far below zero: still a choice and weights that sum to 1
+    bias = torch.randn(E, generator=g) * 2
+    chosen, weights, _ = ops.moe_route(z.cuda(), None, E, top, 1, 1, bias=bias.cuda(), top_first=True)
+    full = (z[:, :E] + bias).double()
+    val, idx = torch.topk(full, top, dim=-1)
+    want_w = torch.softmax(val, dim=-1)
+    got_idx = chosen.cpu().long()
+    order = torch.argsort(got_idx, dim=1)
+    want_order = torch.argsort(idx, dim=1)
+    assert torch.equal(torch.gather(got_idx, 1, order), torch.gather(idx, 1, want_order))
+    _close(torch.gather(weights.cpu(), 1, order), torch.gather(want_w, 1, want_order), "float32")
+    assert float((weights.sum(-1) - 1).abs().max()) < 1e-5
