@@ -996,6 +996,229 @@ def workload_mufevik(steps: int, warmup: int, size: str, batch: int) -> int:
     return 0
 
 
+# Kipizen at the sizes of MUFEVIK_SIZES (the closest design: softmax attention, a matrix-state recurrence and routed
+# experts): eight layers (lightning attention, two layers of window attention of which the second reads the first one's
+# keys and values, lightning, ...); random weights N(0, 0.02), vectors 1 + N(0, 0.02).
+KIPIZEN_WINDOW = 1024
+
+
+def kipizen_config(z: dict) -> dict:
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]}}
+    H = z["lin_heads"]
+    lin = {"type": "lightning", "mlp": mlp,
+           "mixer": {"heads": H, "dim": z["lin_dim"], "vdim": z["lin_vdim"], "decay": [1.0 - 2.0 ** (-1 - 7 * i / max(1, H - 1)) for i in range(H)]}}
+
+    def att(kv_from=None):
+        m = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+             "softcap": 30.0, "mask": {"size": KIPIZEN_WINDOW}, "rot": {"dims": z["dim"] // 2, "base": 10000.0, "scaling": {"factor": 2.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mlp": mlp, "mixer": m}
+    return {"architecture": "Kipizen", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [lin, att(), att(1), lin, lin, att(), att(5), lin]}
+
+
+def build_kipizen(z: dict, max_tokens: int, max_batch: int, context: int):
+    import torch
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.storage import make_storage
+    from cpmcu_b200.loading import build_model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import random_tensors
+
+    arch = architecture("Kipizen")
+    cfg = arch.config_class.from_dict(kipizen_config(z))
+    model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
+    storage = make_storage(model, PREFILL_TOKENS, max_batch, max_tokens=max_tokens, max_seq_tokens=context + 64, n_slots=max_batch + 2)
+    model.load_weights(random_tensors(model.weight_specs(), 6, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    torch.cuda.empty_cache()
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=PREFILL_TOKENS, graph_prompts=True)
+
+
+def kipizen_kernels(z: dict, pk: dict, context: int, batch: int) -> dict:
+    """Every kernel of the design alone, at the size's shapes, beside the like kernel of the closest models (the dense
+    attention with as many key-value heads, Mufevik's rotary store, recurrence with a decay per channel, head norm and
+    routing): a prompt of 2,048 tokens and a decode step of ``batch`` sequences at ``context`` tokens.  CUDA events
+    around one launch after a flush of L2 (a 512 MB buffer is written), median of five; bytes and FLOPs are the
+    algorithmic ones (attention: the keys a window holds)."""
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds, QUERY_TILE_TOKENS, StepContext
+
+    ops = Ops(torch.bfloat16)
+    dev = "cuda:0"
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    W, H, G, d, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    T, win = PREFILL_TOKENS, KIPIZEN_WINDOW
+    i32 = dict(dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for _ in range(6):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[1:])
+
+    def context_of(q_lens, starts, slots):
+        pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
+        seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
+        cu = torch.tensor([0] + [sum(q_lens[:i + 1]) for i in range(len(q_lens))], **i32)
+        kv = [s + n for n, s in zip(q_lens, starts)]
+        ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                          q_lens=list(q_lens), kv_lens=kv, slots=list(slots), max_q_len=max(q_lens), max_kv_len=max(kv),
+                          token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                          kv_len_dev=torch.tensor(kv, **i32), slot_dev=torch.tensor(list(slots), **i32))
+        ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+        tr = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+        ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(tr, **i32), len(ts))
+        return ctx
+
+    out = {}
+
+    def note(name, ms, nbytes=0.0, flops=0.0, like=None):
+        row = {"us": ms * 1e3}
+        if nbytes:
+            row["gbs"] = nbytes / (ms * 1e-3) / 1e9
+            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
+        if flops:
+            row["tflops"] = flops / (ms * 1e-3) / 1e12
+            row["frac_bf16"] = row["tflops"] / pk["bf16_tflops"]
+        if like:
+            row["like"] = like
+        out[name] = row
+
+    n_slots = batch + 2
+    cache = Cache([CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0)], max_tokens=(batch + 1) * (context + 64),
+                  dtype=torch.bfloat16, device=dev, n_slots=n_slots)
+    slots = [cache.open_sequence() for _ in range(batch)]
+    for s_ in slots:
+        cache.reserve(s_, context)
+    cache.sync()
+    lane = cache.lane(0)
+    lane.k.normal_(0, 0.5)
+    lane.v.normal_(0, 0.5)
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    LH, ld, ldv = z["lin_heads"], z["lin_dim"], z["lin_vdim"]
+    wg = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wu = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wd = torch.randn(E, W, ff, device=dev).bfloat16() * 0.02
+    for phase, q_lens, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx = context_of(q_lens, starts, slots[:len(q_lens)])
+        n = ctx.n_tokens
+        keys = [s + j + 1 for nq, s in zip(q_lens, starts) for j in range(nq)]
+        seen = [min(k_, win) for k_ in keys]
+        # window attention with capped scores and a sink, beside the dense attention over the same cache
+        cols = (H + G) * d + G * dv
+        proj = torch.randn(n, cols, device=dev)
+        inv = torch.ones(d // 4, device=dev)
+        bq, bk, bv = torch.zeros(H * d, device=dev), torch.zeros(G * d, device=dev), torch.zeros(G * dv, device=dev)
+        note(f"{phase}/qk_prepare_store (bias, rotation, unit rms, store)",
+             timed(lambda: ops.qk_prepare_store(ctx, proj, lane, H, G, d, dv, (bq, bk, bv), inv, d // 2, True, 1e-5)),
+             n * cols * 6.0, like="rope_store_dv")
+        qkv = torch.randn(n, cols, device=dev).bfloat16()
+        inv2 = torch.ones(d // 2, device=dev)
+        note(f"{phase}/rope_store_dv (Mufevik)", timed(lambda: ops.rope_store_dv(ctx, qkv, lane, H, G, d, dv, inv2, d)), n * cols * 4.0)
+        lane.k.normal_(0, 0.5)
+        q = torch.randn(n, H, d, device=dev).bfloat16()
+        note(f"{phase}/sink_attention (window {win}, cap, sink)",
+             timed(lambda: ops.sink_attention(ctx, q, lane, G, dv, d ** -0.5, win, 30.0, True)),
+             nbytes=(len(q_lens) * min(context, win) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
+             flops=2.0 * H * (d + dv) * sum(seen), like="attention")
+        if d == dv:
+            note(f"{phase}/attention (dense, {G} kv heads, no window)", timed(lambda: ops.attention(ctx, q, lane, G, d ** -0.5)),
+                 nbytes=(sum(s + nq for nq, s in zip(q_lens, starts)) * G * 2 * d * 2.0) if phase == "decode" else 0.0,
+                 flops=4.0 * H * d * sum(keys))
+        # lightning attention, beside the recurrence with a decay per key channel
+        width_in = 2 * LH * ld + 2 * LH * ldv
+        lp = torch.randn(n, width_in, device=dev)
+        note(f"{phase}/silu_columns", timed(lambda: ops.silu_columns(lp, 2 * LH * ld + LH * ldv)), n * (2 * LH * ld + LH * ldv) * 8.0,
+             like="add_rmsnorm")
+        ql, kl, vl = lp[:, :LH * ld], lp[:, LH * ld:2 * LH * ld], lp[:, 2 * LH * ld:2 * LH * ld + LH * ldv]
+        dec = (torch.rand(LH, device=dev) * 0.1 + 0.9).unsqueeze(0).expand(n, LH)
+        lstate = torch.zeros(n_slots, LH, ld, ldv, device=dev)
+        rec_bytes = len(q_lens) * LH * ld * ldv * 8.0 + n * (2 * LH * ld + 2 * LH * ldv) * 4.0
+        note(f"{phase}/linear_recurrence (one decay per head)",
+             timed(lambda: ops.linear_recurrence(ctx, ql, kl, vl, dec, None, lstate, LH, LH, ld, ldv, 1.0)),
+             nbytes=rec_bytes, flops=4.0 * n * LH * ld * ldv, like="linear_recurrence (decay per channel)")
+        al2 = torch.rand(n, LH * ld, device=dev) * 0.1 + 0.9
+        qc, kc, vc = (t.contiguous() for t in (ql, kl, vl))
+        note(f"{phase}/linear_recurrence (decay per channel, Mufevik)",
+             timed(lambda: ops.linear_recurrence(ctx, qc, kc, vc, al2, None, lstate, LH, LH, ld, ldv, ld ** -0.5, vector_decay=True)),
+             nbytes=rec_bytes + n * LH * ld * 4.0, flops=4.0 * n * LH * ld * ldv)
+        o = torch.randn(n, LH, ldv, device=dev)
+        gate = lp[:, 2 * LH * ld + LH * ldv:]
+        wall, wv = torch.ones(LH * ldv, device=dev), torch.ones(ldv, device=dev)
+        note(f"{phase}/gated_group_norm (all heads, sigmoid gate)", timed(lambda: ops.gated_group_norm(o, gate, wall, 1e-5, LH, "sigmoid")),
+             n * LH * ldv * 10.0, like="gated_head_norm")
+        note(f"{phase}/gated_head_norm (Mufevik)", timed(lambda: ops.gated_head_norm(o, gate, wv, 1e-5)), n * LH * ldv * 10.0)
+        # the residual and norm, and routed experts
+        x1 = torch.randn(n, W, device=dev)
+        y = torch.randn(n, W, device=dev).bfloat16()
+        wn = torch.ones(W, device=dev)
+        note(f"{phase}/add_rmsnorm (32-bit residual)", timed(lambda: ops.add_rmsnorm(x1, y, 1.0, wn, 1e-5)), n * W * 12.0)
+        logits = torch.randn(n, E, device=dev)
+        rb = torch.zeros(E, device=dev)
+        note(f"{phase}/moe_route (largest logits, softmax over the chosen)",
+             timed(lambda: ops.moe_route(logits, None, E, top, 1, 1, bias=rb, top_first=True)), n * E * 4.0, like="moe_route")
+        logits1 = torch.randn(n, E + 1, device=dev)
+        note(f"{phase}/moe_route (Mufevik: scores, groups, correction)",
+             timed(lambda: ops.moe_route(logits1, rb, E, top, z["groups"], z["keep"], E)), n * (E + 1) * 4.0)
+        chosen, weights, _ = ops.moe_route(logits, None, E, top, 1, 1, bias=rb, top_first=True)
+        used = int(torch.unique(chosen).numel())
+        note(f"{phase}/moe_experts (the kernels Mufevik uses)", timed(lambda: ops.moe_experts(y, chosen, wg, wu, wd)),
+             nbytes=used * 3.0 * ff * W * 2.0 + n * top * (W + ff) * 4.0, flops=6.0 * n * top * ff * W)
+        pairs = ops.moe_experts(y, chosen, wg, wu, wd)
+        note(f"{phase}/moe_combine", timed(lambda: ops.moe_combine(pairs, weights, None, None)), n * W * 2.0 * (top + 1))
+    return out
+
+
+def workload_kipizen(steps: int, warmup: int, size: str, batch: int) -> int:
+    """Kipizen at one of MUFEVIK_SIZES beside Mufevik at the same sizes (the closest design): decode steps of ``batch``
+    sequences ending at a context of 4,096 tokens under a CUDA graph, a prompt of 2,048 tokens, and every kernel of the
+    design alone beside its like."""
+    import torch
+
+    z, pk, context = MUFEVIK_SIZES[size], peaks(), CONTEXT
+    cfg, model, cache, stepper = build_kipizen(z, batch * (context + 64) + 128, batch, context)
+    pre_ms = time_prefill_any(stepper, cfg.vocab)
+    ms, clocks, launches, cache_bytes = time_decode(stepper, batch, steps, warmup, cfg.vocab, True, context=context)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    del model, cache, stepper
+    torch.cuda.empty_cache()
+    mcfg, mmodel, mcache, mstepper = build_mufevik(z, batch * (context + 64) + 128, batch, context)
+    m_pre = time_prefill_any(mstepper, mcfg.vocab)
+    m_ms, _, m_launches, m_cache = time_decode(mstepper, batch, steps, warmup, mcfg.vocab, False, context=context)
+    m_weights = mmodel.weight_bytes_per_step()
+    m_achieved = (m_weights + m_cache) / (m_ms * 1e-3) / 1e9
+    del mmodel, mcache, mstepper
+    torch.cuda.empty_cache()
+    kernels = kipizen_kernels(z, pk, context, batch)
+    print(json.dumps({
+        "workload": "kipizen", "metric": f"decode tokens/s (Kipizen {size} sizes, bf16, batch {batch}, context {context})",
+        "value": batch * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 6",
+        "config": dict(z, size=size, layers=len(cfg.layers), window=KIPIZEN_WINDOW, global_batch=batch, seq_len=context,
+                       prefill_tokens=PREFILL_TOKENS, cuda_graph=True, peaks=pk["source"]),
+        "prefill": {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "ms": pre_ms},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "weight_bytes": weight_bytes, "cache_bytes": cache_bytes},
+        "closest_model": {"model": f"Mufevik at the {size} sizes, {len(mcfg.layers)} layers",
+                          "decode_tokens_s": batch * 1000.0 / m_ms, "ms_per_step": m_ms, "prefill_tokens_s": PREFILL_TOKENS / (m_pre * 1e-3),
+                          "prefill_ms": m_pre, "roofline_frac": m_achieved / pk["hbm_gbs"], "weight_bytes": m_weights,
+                          "cache_bytes": m_cache, "gpu_launches": m_launches},
+        "kernels": kernels, "clocks": clocks, "gpu_launches": launches,
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1004,12 +1227,12 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik", "mufevik"],
+    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik", "mufevik", "kipizen"],
                     help="dense8b: the headline line (8B sizes, batch 8, context 4096); half_b: 0.5B sizes, batch 64, prompts "
                          "uniform in [64, 2048] chunked at 512, decode at context 8192 (256 steps by default); sparse8b: 8B "
                          "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps; reravik: the Reravik "
                          "design at --size beside MiniCPM4 of equal sizes, and its kernels alone; mufevik: the same for the Mufevik design "
-                         "(sizes 1k and 2k)")
+                         "(sizes 1k and 2k); kipizen: the Kipizen design beside Mufevik at the same sizes (1k and 2k), and its kernels alone")
     ap.add_argument("--size", default="2k", choices=sorted(RERAVIK_SIZES), help="--workload reravik / mufevik: which layer sizes")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
     ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
@@ -1037,6 +1260,11 @@ def main() -> int:
             print(f"bench.py: --workload mufevik takes --size {' or '.join(sorted(MUFEVIK_SIZES))}")
             return 2
         return workload_mufevik(a.steps, max(3, a.warmup), a.size, a.batch)
+    if a.workload == "kipizen":
+        if a.size not in MUFEVIK_SIZES:
+            print(f"bench.py: --workload kipizen takes --size {' or '.join(sorted(MUFEVIK_SIZES))}")
+            return 2
+        return workload_kipizen(a.steps, max(3, a.warmup), a.size, a.batch)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)
