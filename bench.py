@@ -1131,6 +1131,10 @@ def kipizen_kernels(z: dict, pk: dict, context: int, batch: int) -> dict:
              timed(lambda: ops.sink_attention(ctx, q, lane, G, dv, d ** -0.5, win, 30.0, True)),
              nbytes=(len(q_lens) * min(context, win) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
              flops=2.0 * H * (d + dv) * sum(seen), like="attention")
+        note(f"{phase}/sink_attention (no window: the keys of the dense kernel; cap, sink)",
+             timed(lambda: ops.sink_attention(ctx, q, lane, G, dv, d ** -0.5, 0, 30.0, True)),
+             nbytes=(sum(keys) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
+             flops=2.0 * H * (d + dv) * sum(keys), like="attention")
         if d == dv:
             note(f"{phase}/attention (dense, {G} kv heads, no window)", timed(lambda: ops.attention(ctx, q, lane, G, d ** -0.5)),
                  nbytes=(sum(s + nq for nq, s in zip(q_lens, starts)) * G * 2 * d * 2.0) if phase == "decode" else 0.0,

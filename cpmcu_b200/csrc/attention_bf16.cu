@@ -132,17 +132,7 @@ __device__ __forceinline__ void attend_page(TileState<D>& st, const uint4 (&q)[2
 // depend on how the compiler orders loads.  The 16-byte chunks of odd rows are stored
 // shifted by four chunks where rows are a multiple of 128 bytes apart, which keeps the
 // fragment reads free of bank conflicts.
-__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(smem_addr), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
-__device__ __forceinline__ uint4 lds16(uint32_t smem_addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
-    return v;
-}
+// (cp_async16, cp_async_commit, cp_async_wait and lds16 are in mma_bf16.cuh)
 
 constexpr int kDecodeStages = 2;
 

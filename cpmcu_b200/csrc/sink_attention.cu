@@ -236,22 +236,23 @@ __device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint3
     lo = pack_bf16(a - __low2float(h), b - __high2float(h));
 }
 
-// 32 keys key0 .. key0 + 31 of one page (khalf: their rows of the key page; vhalf: value page + their token offset).
-// Row r sees key when lo[r] <= key <= hi[r].
-template <int D, int DV>
-__device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (&q)[2][D / 32], const bf16* __restrict__ khalf,
-                                                 const bf16* __restrict__ vhalf, int key0, const int (&lo)[2],
-                                                 const int (&hi)[2], float scale, float cap, int lane) {
+// 32 keys key0 .. key0 + 31 of one page; row r sees a key when lo[r] <= key <= hi[r].  The fragment loads:
+// ``kload(t, w)`` gives the 8 channels 32 w + 8 j ... of key 8 (n / 2) + 2 t + (n & 1) of the 32, ``vload(nt)`` the
+// 8 tokens 8 j ... of value channel 8 nt + n  (j = lane % 4, n = lane / 4).
+template <int D, int DV, typename KLoad, typename VLoad>
+__device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (&q)[2][D / 32], KLoad kload, VLoad vload,
+                                                 int key0, const int (&lo)[2], const int (&hi)[2], float scale, float cap,
+                                                 int lane) {
     constexpr float kLog2e = 1.4426950408889634f;
-    const int j = lane & 3, n = lane >> 2;
+    const int j = lane & 3;
     float s[4][4];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-        s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
-        const bf16* kp = khalf + (8 * (n >> 1) + 2 * t + (n & 1)) * D + 8 * j;
+    for (int t = 0; t < 4; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
 #pragma unroll
-        for (int w = 0; w < D / 32; ++w) {
-            const uint4 kv = ldg16(kp + 32 * w);
+    for (int w = 0; w < D / 32; ++w) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint4 kv = kload(t, w);
             mma_16816(s[t], q[0][w].x, q[1][w].x, q[0][w].y, q[1][w].y, kv.x, kv.y);
             mma_16816(s[t], q[0][w].z, q[1][w].z, q[0][w].w, q[1][w].w, kv.z, kv.w);
         }
@@ -304,14 +305,20 @@ __device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (
     split_bf16(s[2][2], s[2][3], ch[1], cl[1]);
     split_bf16(s[3][0], s[3][1], ch[2], cl[2]);
     split_bf16(s[3][2], s[3][3], ch[3], cl[3]);
-    const bf16* vp = vhalf + n * kPageTokens + 8 * j;
+    // four output tiles at a time: their loads, then their products, so that products into one accumulator lie apart
 #pragma unroll
-    for (int nt = 0; nt < DV / 8; ++nt) {
-        const uint4 vv = ldg16(vp + nt * 8 * kPageTokens);
-        mma_16816(st.o[nt], ah[0], ah[1], ah[2], ah[3], vv.x, vv.y);
-        mma_16816(st.o[nt], ch[0], ch[1], ch[2], ch[3], vv.z, vv.w);
-        mma_16816(st.o[nt], al[0], al[1], al[2], al[3], vv.x, vv.y);
-        mma_16816(st.o[nt], cl[0], cl[1], cl[2], cl[3], vv.z, vv.w);
+    for (int nt0 = 0; nt0 < DV / 8; nt0 += 4) {
+        uint4 vv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vv[i] = vload(nt0 + i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], ah[0], ah[1], ah[2], ah[3], vv[i].x, vv[i].y);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], ch[0], ch[1], ch[2], ch[3], vv[i].z, vv[i].w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], al[0], al[1], al[2], al[3], vv[i].x, vv[i].y);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], cl[0], cl[1], cl[2], cl[3], vv[i].z, vv[i].w);
     }
 }
 
@@ -336,8 +343,21 @@ __device__ __forceinline__ void sink_finish(SinkTile<DV>& st, int sink, int lane
 }
 
 // Prompt tokens: a block of 4 warps takes 64 consecutive query tokens of one sequence and one head, 16 a warp (the
-// tile lists of the plain prefill kernel).  A warp walks from the first key its first token sees to its last token.
+// tile lists of the plain prefill kernel).  The block walks the pages from the first key its first token sees to its
+// last token; a key page and a value page come into shared memory once (cp.async, two pages in flight) and are read
+// by the 4 warps, each of which passes over the halves of a page that none of its own rows sees.  The 16-byte chunks
+// of odd rows lie shifted by four chunks where rows are a multiple of 128 bytes apart (fragment reads without bank
+// conflicts).
 constexpr int kSinkTileWarps = 4;
+constexpr int kSinkTileRows = kSinkTileWarps * 16;
+
+template <int D, int DV>
+struct SinkStage {
+    static constexpr int kKeyChunks = D / 8;                              // 16-byte chunks of a key row
+    static constexpr bool kSwizzleKeys = kKeyChunks % 8 == 0;
+    static constexpr int kKeyBytes = kPageTokens * D * 2;
+    static constexpr int kBytes = kKeyBytes + DV * kPageTokens * 2;       // a key page and a value page
+};
 
 template <int D, int DV>
 __global__ void __launch_bounds__(kSinkTileWarps * 32)
@@ -346,18 +366,50 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
                             const int* __restrict__ page_table, int max_pages, int window, int n_heads, int n_kv, float scale,
                             float cap, int sink) {
+    using S = SinkStage<D, DV>;
+    extern __shared__ __align__(128) unsigned char sink_smem[];
+    const uint32_t stages = (uint32_t)__cvta_generic_to_shared(sink_smem);
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = lane & 3, g = lane >> 2;
-    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int tile = gridDim.y - 1 - blockIdx.y;                 // later tiles of a sequence see more keys: they go first
     const int seq = tile_seq[tile], h = blockIdx.x;
     const int kvh = h / (n_heads / n_kv);
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-    const int row0 = tile_row[tile] + 16 * warp;
-    if (row0 >= q_len) return;
-    const int history = kv_len[seq] - q_len;
+    const int tile_row0 = tile_row[tile];
+    const int row0 = tile_row0 + 16 * warp;                      // first of this warp's 16 tokens
+    const int history = kv_len[seq] - q_len;                     // keys cached before this step's tokens
     const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+    // the block's keys, and this warp's (empty when the warp has no rows)
+    const int first_page = (window > 0 ? max(0, history + tile_row0 - window + 1) : 0) / kPageTokens;
+    const int last_page = (history + min(tile_row0 + kSinkTileRows, q_len) - 1) / kPageTokens;
+    const int my_first = window > 0 ? max(0, history + row0 - window + 1) : 0;
+    const int my_last = row0 < q_len ? history + min(row0 + 16, q_len) - 1 : -1;
+
+    auto issue = [&](int p) {
+        if (p <= last_page) {
+            const int page = CPM_PAGE(pages, p, max_pages);
+            const bf16* kpage = k_cache + page_row_offset(page, kvh, 0, n_kv, D);
+            const bf16* vpage = v_cache + value_offset(page, kvh, 0, 0, n_kv, DV);
+            const uint32_t stage = stages + ((p - first_page) & 1) * S::kBytes;
+#pragma unroll 4
+            for (int c = threadIdx.x; c < kPageTokens * S::kKeyChunks; c += kSinkTileWarps * 32) {
+                const int row = c / S::kKeyChunks, col = c % S::kKeyChunks;
+                const int pcol = S::kSwizzleKeys ? (col ^ ((row & 1) << 2)) : col;
+                cp_async16(stage + (row * S::kKeyChunks + pcol) * 16, kpage + c * 8);
+            }
+#pragma unroll 4
+            for (int c = threadIdx.x; c < DV * 8; c += kSinkTileWarps * 32) {
+                const int row = c >> 3, col = c & 7;                       // a value row holds 64 tokens = 8 chunks
+                cp_async16(stage + S::kKeyBytes + (row * 8 + (col ^ ((row & 1) << 2))) * 16, vpage + c * 8);
+            }
+        }
+        cp_async_commit();
+    };
+    issue(first_page);
+    issue(first_page + 1);
+
     uint4 qf[2][D / 32];
     int lo[2], hi[2];
 #pragma unroll
@@ -366,19 +418,39 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const bool valid = row < q_len;
         hi[r] = valid ? history + row : -1;
         lo[r] = (valid && window > 0) ? max(0, hi[r] - window + 1) : 0;
-        const bf16* qrow = q + ((int64_t)(q_begin + (valid ? row : row0)) * n_heads + h) * D + 8 * j;
+        const bf16* qrow = q + ((int64_t)(q_begin + (valid ? row : 0)) * n_heads + h) * D + 8 * j;
 #pragma unroll
         for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
     }
     SinkTile<DV> st;
     st.init();
-    const int first = window > 0 ? max(0, history + row0 - window + 1) : 0;
-    const int last = history + min(row0 + 16, q_len) - 1;
-    for (int key0 = first & ~31; key0 <= last; key0 += 32) {
-        const int page = CPM_PAGE(pages, key0 / kPageTokens, max_pages), off = key0 % kPageTokens;
-        sink_attend_keys<D, DV>(st, qf, k_cache + page_row_offset(page, kvh, off, n_kv, D),
-                                v_cache + value_offset(page, kvh, 0, off, n_kv, DV), key0, lo, hi, scale, cap, lane);
+    for (int p = first_page; p <= last_page; ++p) {
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t stage = stages + ((p - first_page) & 1) * S::kBytes;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int key0 = p * kPageTokens + 32 * u;
+            if (key0 + 31 < my_first || key0 > my_last) continue;          // the same for the whole warp
+            const int krow = 32 * u + 8 * (g >> 1) + (g & 1);
+            sink_attend_keys<D, DV>(
+                st, qf,
+                [&](int t, int w) {
+                    const int row = krow + 2 * t;
+                    const int swz = S::kSwizzleKeys ? ((row & 1) << 2) : 0;
+                    return lds16(stage + (row * S::kKeyChunks + ((4 * w + j) ^ swz)) * 16);
+                },
+                [&](int nt) {
+                    const int row = 8 * nt + g;
+                    return lds16(stage + S::kKeyBytes + (row * 8 + ((4 * u + j) ^ ((row & 1) << 2))) * 16);
+                },
+                key0, lo, hi, scale, cap, lane);
+        }
+        __syncthreads();
+        issue(p + 2);
     }
+    cp_async_wait<0>();
+    if (row0 >= q_len) return;
     sink_finish<DV>(st, sink, lane, [&](int r) -> bf16* {
         const int row = row0 + g + 8 * r;
         return row < q_len ? out + ((int64_t)(q_begin + row) * n_heads + h) * DV : nullptr;
@@ -395,7 +467,7 @@ __global__ void __launch_bounds__(kSinkTokenWarps * 32)
 sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                             bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages, int window,
-                            int n_heads, int n_kv, float scale, float cap, int sink) {
+                            int n_heads, int n_kv, float scale, float cap, int sink, float* __restrict__ shares) {
     __shared__ float part_o[kSinkTokenWarps - 1][16][DV + 1];
     __shared__ float part_ml[kSinkTokenWarps - 1][16][2];
     pdl_launch_dependents();
@@ -423,14 +495,19 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     SinkTile<DV> st;
     st.init();
     const int first = (window > 0 ? max(0, p - window + 1) : 0) & ~31;
+    // the token's steps of 32 keys go to gridDim.z blocks (shares != null when more than one), a block's to its warps
     const int n_blocks = (p - first) / 32 + 1;
-    const int share = (n_blocks + kSinkTokenWarps - 1) / kSinkTokenWarps;
-    const int b_end = min(n_blocks, (warp + 1) * share);
-    for (int b = warp * share; b < b_end; ++b) {
+    const int per_block = (n_blocks + gridDim.z - 1) / gridDim.z;
+    const int blk_begin = blockIdx.z * per_block, blk_end = min(n_blocks, blk_begin + per_block);
+    const int share = (max(0, blk_end - blk_begin) + kSinkTokenWarps - 1) / kSinkTokenWarps;
+    const int b_end = min(blk_end, blk_begin + (warp + 1) * share);
+    for (int b = blk_begin + warp * share; b < b_end; ++b) {
         const int key0 = first + 32 * b;
         const int page = CPM_PAGE(pages, key0 / kPageTokens, max_pages), off = key0 % kPageTokens;
-        sink_attend_keys<D, DV>(st, qf, k_cache + page_row_offset(page, kvh, off, n_kv, D),
-                                v_cache + value_offset(page, kvh, 0, off, n_kv, DV), key0, lo, hi, scale, cap, lane);
+        const bf16* kp = k_cache + page_row_offset(page, kvh, off + 8 * (g >> 1) + (g & 1), n_kv, D) + 8 * j;
+        const bf16* vp = v_cache + value_offset(page, kvh, g, off + 8 * j, n_kv, DV);
+        sink_attend_keys<D, DV>(st, qf, [&](int t, int w) { return ldg16(kp + 2 * t * D + 32 * w); },
+                                [&](int nt) { return ldg16(vp + nt * 8 * kPageTokens); }, key0, lo, hi, scale, cap, lane);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -478,8 +555,16 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                 st.o[nt][2 * r + 1] = fmaf(part_o[w][row][8 * nt + 2 * j + 1], f, st.o[nt][2 * r + 1]);
             }
         }
-        if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
         if (row >= rows) continue;
+        if (shares != nullptr) {            // this block's share as it is: the accumulator, the maximum it refers to, the sum
+            float* dst = shares + (((int64_t)blockIdx.z * gridDim.x + t) * n_heads + h0 + row) * (DV + 2);
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt)
+                *reinterpret_cast<float2*>(dst + 8 * nt + 2 * j) = make_float2(st.o[nt][2 * r], st.o[nt][2 * r + 1]);
+            if (j == 0) *reinterpret_cast<float2*>(dst + DV) = make_float2(m, l);
+            continue;
+        }
+        if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* orow = out + ((int64_t)t * n_heads + h0 + row) * DV + 2 * j;
 #pragma unroll
@@ -488,20 +573,62 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 }
 
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / (sink 2^(-M) + sum_s l_s 2^(m_s - M)), M = max_s m_s, over the shares s of a
+// token's keys (rows of dv + 2 floats: o, m, l).  One warp per token and head.
+__global__ void sink_combine_shares_kernel(const float* __restrict__ shares, bf16* __restrict__ out, int n_rows, int dv,
+                                           int n_splits, int sink) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const int64_t stride = (int64_t)n_rows * (dv + 2);
+    const float* mine = shares + (int64_t)row * (dv + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, mine[s * stride + dv]);
+    const float use = m == -INFINITY ? 0.f : m;
+    float l = 0.f, o[8];                       // channels lane, lane + 32, ... (dv <= 256)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float* src = mine + s * stride;
+        const float f = exp2f(src[dv] - use);
+        l = fmaf(src[dv + 1], f, l);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i < dv) o[i] = fmaf(src[lane + 32 * i], f, o[i]);
+    }
+    if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (lane + 32 * i < dv) out[(int64_t)row * dv + lane + 32 * i] = __float2bfloat16(o[i] * inv);
+}
+
 template <int D, int DV>
 static int launch_sink_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                             const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* positions,
                             const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
-                            int n_tokens, int n_heads, int n_kv, float scale, float cap, int sink, cudaStream_t stream) {
+                            int n_tokens, int n_heads, int n_kv, float scale, float cap, int sink, float* shares,
+                            int n_splits, cudaStream_t stream) {
     if (n_tiles > 0) {
-        cpm_launch(kLaunchAttention, sink_attention_tiles_kernel<D, DV>, dim3(n_heads, n_tiles), dim3(kSinkTileWarps * 32), 0,
+        auto kern = sink_attention_tiles_kernel<D, DV>;
+        constexpr int smem = 2 * SinkStage<D, DV>::kBytes;
+        static bool configured[kMaxDevices] = {};            // per kernel and per device
+        if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
+        cpm_launch(kLaunchAttention, kern, dim3(n_heads, n_tiles), dim3(kSinkTileWarps * 32), smem,
                    stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q,
                    kv_len, slots, page_table, max_pages, window, n_heads, n_kv, scale, cap, sink);
     } else {
         const int group = n_heads / n_kv;
-        cpm_launch(kLaunchAttention, sink_attention_token_kernel<D, DV>, dim3(n_tokens, n_kv * ((group + 15) / 16)),
-                   dim3(kSinkTokenWarps * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                   (bf16*)out, positions, token_seq, slots, page_table, max_pages, window, n_heads, n_kv, scale, cap, sink);
+        cpm_launch(kLaunchAttention, sink_attention_token_kernel<D, DV>,
+                   dim3(n_tokens, n_kv * ((group + 15) / 16), n_splits), dim3(kSinkTokenWarps * 32), 0, stream, (const bf16*)q,
+                   (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages,
+                   window, n_heads, n_kv, scale, cap, sink, n_splits > 1 ? shares : (float*)nullptr);
+        if (n_splits > 1) {
+            const int n_rows = n_tokens * n_heads;
+            cpm_launch(kLaunchAttention, sink_combine_shares_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream,
+                       (const float*)shares, (bf16*)out, n_rows, DV, n_splits, sink);
+        }
     }
     return launch_status();
 }
@@ -512,21 +639,23 @@ CPM_API int cpm_sink_attention_bf16_sizes(int d, int dv) {
 }
 
 // bf16 q [tokens, heads, d] -> out [tokens, heads * dv].  With n_tiles > 0 the tokens are prompt tokens packed by
-// sequence (cu_q, kv_len, tile lists of 64 rows); else every token is taken alone by its position and sequence.
+// sequence (cu_q, kv_len, tile lists of 64 rows); else every token is taken alone by its position and sequence, its keys
+// shared out over n_splits blocks (n_splits > 1: shares holds n_splits * tokens * heads * (dv + 2) floats).
 CPM_API int cpm_sink_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                                     const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len,
                                     const int* positions, const int* token_seq, const int* slots, const int* page_table,
                                     int max_pages, int window, int n_tokens, int n_heads, int n_kv, int d, int dv, float scale,
-                                    float cap, int sink, cudaStream_t stream) {
+                                    float cap, int sink, float* shares, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (!cpm_sink_attention_bf16_sizes(d, dv) || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || n_tiles > 65535)
+    if (!cpm_sink_attention_bf16_sizes(d, dv) || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || n_tiles > 65535 ||
+        n_splits < 1 || n_splits > 65535 || (n_splits > 1 && !shares))
         return CPM_BAD_ARGUMENT;
     if (n_tiles > 0 ? (!tile_seq || !tile_row || !cu_q || !kv_len) : (!positions || !token_seq)) return CPM_BAD_ARGUMENT;
 #define CPM_SINK_CASE(DD, VV)                                                                                              \
     if (d == DD && dv == VV)                                                                                               \
         return launch_sink_bf16<DD, VV>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, positions,    \
                                         token_seq, slots, page_table, max_pages, window, n_tokens, n_heads, n_kv, scale,   \
-                                        cap, sink, stream);
+                                        cap, sink, shares, n_splits, stream);
 #define CPM_SINK_ROW(DD) CPM_SINK_CASE(DD, 32) CPM_SINK_CASE(DD, 64) CPM_SINK_CASE(DD, 96) CPM_SINK_CASE(DD, 128)
     CPM_SINK_ROW(32) CPM_SINK_ROW(64) CPM_SINK_ROW(96) CPM_SINK_ROW(128)
 #undef CPM_SINK_ROW

@@ -928,6 +928,17 @@ class Ops:
             return self.sink_attention_bf16(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
         return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
 
+    SINK_MAX_SPLITS = 16
+
+    def sink_attention_splits(self, ctx, n_tokens: int, n_heads: int, n_kv: int, window: int) -> int:
+        """Blocks that share the keys of a token taken alone: none while the tokens fill the device; else enough for
+        about two blocks an SM, as long as each of a block's four warps keeps at least two steps of 32 keys."""
+        blocks = n_tokens * n_kv * ((n_heads // n_kv + 15) // 16)
+        if blocks * 2 > self.sm_count:
+            return 1
+        keys = min(window, ctx.max_kv_len) if window else ctx.max_kv_len      # in a recorded step an upper bound
+        return max(1, min(self.SINK_MAX_SPLITS, 2 * self.sm_count // blocks, ((keys + 31) // 32) // 8))
+
     SINK_TILE_MIN_ROWS = 8       # shorter portions than this go token by token (a tile of 16 rows would be mostly empty)
 
     def sink_attention_bf16(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
@@ -940,11 +951,16 @@ class Ops:
         out = self.empty(n, n_heads * dv)
         tiles = None if ctx.is_decode or ctx.max_q_len < self.SINK_TILE_MIN_ROWS else ctx.q_tiles
         tile_seq, tile_row, n_tiles = tiles if tiles is not None else (None, None, 0)
+        n_splits, shares = 1, None
+        if n_tiles == 0:
+            n_splits = self.sink_attention_splits(ctx, n, n_heads, n_kv, int(window))
+            if n_splits > 1:
+                shares = self.empty(n_splits * n * n_heads * (dv + 2), dtype=torch.float32)
         check(self.lib.cpm_sink_attention_bf16(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(tile_seq), _ptr(tile_row),
                                                int(n_tiles), _ptr(ctx.cu_q), _ptr(ctx.kv_len_dev), _ptr(ctx.positions),
                                                _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
                                                lane.page_table.shape[1], int(window), n, n_heads, n_kv, d, dv, float(scale),
-                                               float(cap), 1 if sink else 0, self._stream()),
+                                               float(cap), 1 if sink else 0, _ptr(shares), n_splits, self._stream()),
               f"sink attention on tensor cores ({n_heads} heads, {d} / {dv})")
         return out
 

@@ -415,6 +415,59 @@ def test_sink_window_attention_batches_unequal_sequences(dtype):
         _close(torch.cat(got[i]), want[i][:done[i]], dtype)
 
 
+@pytest.mark.parametrize("H,G,d,dv,window,sink", [(6, 2, 64, 64, 700, True), (4, 1, 128, 32, None, True), (20, 1, 32, 128, 1000, False)])
+def test_single_tokens_whose_keys_are_shared_among_blocks(H, G, d, dv, window, sink):
+    """Two sequences of unequal lengths bring one token each; the keys of a token are divided among 1, 3 and 16 blocks
+    and by the library's own choice.  The score towers at a far key (the last one the window holds, or the first key)
+    for one sequence and at the query's own key for the other, so that a share that is lost or counted twice shows;
+    the shorter sequence leaves most shares of 16 empty."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(d + dv)
+    lens, scale, cap = [1500, 45], 0.2, 25.0
+    data = [(torch.randn(n, H, d, generator=g) * 0.5, torch.randn(n, G, d, generator=g) * 0.5, torch.randn(n, G, dv, generator=g))
+            for n in lens]
+    far = lens[0] - window if window else 0
+    data[0][0][-1, :, 3] = 9.0
+    data[0][1][far, :, 3] = 9.0
+    if far > 0:
+        data[0][1][far - 1, :, 3] = 30.0                                      # the first key the window has dropped
+    data[1][0][-1, :, 5] = 9.0
+    data[1][1][-1, :, 5] = 9.0
+    rnd = lambda t: t.bfloat16().double()
+    want = torch.cat([plain.window_attention_core(rnd(q), rnd(k), rnd(v), scale, cap, window, sink)[-1:].reshape(1, H * dv)
+                      for q, k, v in data])
+    cache = Cache([CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0, window=window)], max_tokens=64 * 30,
+                  dtype=torch.bfloat16, device="cuda:0", n_slots=3)
+    cache.open_sequence()
+    slots = [cache.open_sequence() for _ in lens]
+    lane = cache.lane(0)
+    for (q, k, v), n, slot in zip(data, lens, slots):                         # all but the last token, as a prompt
+        cache.reserve(slot, n)
+        cache.sync()
+        ctx = _ctx([n - 1], [0], [slot])
+        proj = torch.cat([t[:n - 1].reshape(n - 1, -1) for t in (q, k, v)], dim=1).bfloat16().float().cuda().contiguous()
+        ops.qk_prepare_store(ctx, proj, lane, H, G, d, dv, (None, None, None), None, 0, False, 0.0)
+    ctx = _ctx([1, 1], [n - 1 for n in lens], slots)
+    proj = torch.cat([torch.cat([t[-1:].reshape(1, -1) for t in seq], dim=1) for seq in data]).bfloat16().float().cuda().contiguous()
+    qr = ops.qk_prepare_store(ctx, proj, lane, H, G, d, dv, (None, None, None), None, 0, False, 0.0)
+    assert ops.sink_attention_splits(ctx, 2, H, G, window or 0) > 1
+    choose = ops.sink_attention_splits
+    try:
+        for n_splits in (None, 1, 3, 16):
+            if n_splits is not None:
+                ops.sink_attention_splits = lambda *a, n_splits=n_splits: n_splits
+            got = ops.sink_attention_bf16(ctx, qr, lane, G, dv, scale, window or 0, cap, sink)
+            _close(got, want, "bfloat16")
+            _close(got[0], want[0], "bfloat16")
+            _close(got[1], want[1], "bfloat16")
+    finally:
+        ops.sink_attention_splits = choose
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,dv,rot_dim,base,factor", [(4, 2, 64, 64, 32, 20000.0, 2.0), (3, 1, 24, 40, 24, 300.0, 1.0),
                                                             (2, 2, 128, 32, 0, 1.0, 1.0), (5, 5, 20, 20, 8, 1e6, 7.5)])
