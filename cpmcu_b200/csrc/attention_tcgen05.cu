@@ -90,7 +90,17 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-template <int kD>
+// What the sink window attention adds to the kernel below (kSink): keys no further back than ``window`` tokens
+// (0: all), scores capped as cap * tanh(s / cap) (cap_log2 = cap * log2(e), 0: no cap; pre = scale / cap), and a sink of
+// score 0 without a value in the softmax's denominator.
+struct SinkExtras {
+    int window;
+    float cap_log2;
+    float pre;
+    int sink;
+};
+
+template <int kD, bool kSink>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
@@ -98,7 +108,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                  const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
                                  int n_pages, int n_heads, int n_kv, float scale_log2, float* __restrict__ part_o,
-                                 float* __restrict__ part_ml, int n_splits, int n_tokens, int v_shift) {
+                                 float* __restrict__ part_ml, int n_splits, int n_tokens, int v_shift,
+                                 const SinkExtras extras) {
     using Z = Sizes<kD>;
     constexpr int kTileBytes = Z::kTileBytes;
     extern __shared__ unsigned char smem_raw[];
@@ -120,10 +131,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int last_page = (n_keys - 1) / kPageTokens;
     // With n_splits > 1 (few query tiles, many keys: a short chunk after a long history) the key steps of a tile
     // are shared out over gridDim.z blocks, which leave unnormalised partial results for a second kernel.
-    const int all_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys;
+    // With a window the tile's first key step is the one that holds the first key of its first token.
+    const int window = kSink ? extras.window : 0;
+    const int step0 = window > 0 ? max(0, history + tile_row0 - window + 1) / kBlockKeys : 0;
+    const int all_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys - step0;
     const int per_split = (all_blocks + n_splits - 1) / n_splits;
-    const int j_first = (int)blockIdx.z * per_split;
-    const int n_blocks = max(0, min(all_blocks, j_first + per_split) - j_first);      // key steps of this block
+    const int j_first = step0 + (int)blockIdx.z * per_split;
+    const int n_blocks = max(0, min(step0 + all_blocks, j_first + per_split) - j_first);      // key steps of this block
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzled tiles want 1 KiB alignment
@@ -261,6 +275,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int r = quarter * 32 + lane;
         const int row = tile_row0 + r;
         const int limit = row < q_len ? history + row : -1;      // last key this row may see
+        const int first = (window > 0 && limit >= 0) ? max(0, limit - window + 1) : 0;      // and the first
+        const float sl2 = (kSink && extras.cap_log2 > 0.f) ? 1.f : scale_log2;      // capped scores are in log2 units already
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_addr = lane_base + i * 128, o_addr = lane_base + Z::kOCol0 + i * kD;
         float m_ref = -INFINITY, l = 0.f;
@@ -278,7 +294,29 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int c = 0; c < 4; ++c) tmem_load_32cols(s_addr + c * 32, v[c]);
             tmem_load_wait();
             const int key0 = (j_first + j) * kBlockKeys;
-            if (key0 + kBlockKeys - 1 > history + tile_row0) {   // the diagonal, or the end of the keys
+            if constexpr (kSink) {
+                if (extras.cap_log2 > 0.f) {
+                    // cap * tanh(s / cap) in log2 units, tanh(x) = 1 - 2 / (e^(2x) + 1): exact limits at both ends
+                    const float c2 = 2.f * 1.4426950408889634f * extras.pre, minus2cap = -2.f * extras.cap_log2;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            float rcp;
+                            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(ex2(__uint_as_float(v[c][e]) * c2) + 1.f));
+                            v[c][e] = __float_as_uint(fmaf(minus2cap, rcp, extras.cap_log2));
+                        }
+                }
+                // the diagonal or the end of the keys, and the step in which some row's window begins
+                if (key0 + kBlockKeys - 1 > history + tile_row0 ||
+                    (window > 0 && key0 < history + tile_row0 + kTileRows - window)) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (key0 + c * 32 + e > limit || key0 + c * 32 + e < first) v[c][e] = 0xff800000u;      // -inf
+                }
+            } else if (key0 + kBlockKeys - 1 > history + tile_row0) {   // the diagonal, or the end of the keys
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -290,7 +328,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
-            const float m_new = mx * scale_log2;
+            const float m_new = mx * sl2;
             const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
                 const float alpha = grow ? ex2(m_ref - m_new) : 1.f;     // 0 the first time
@@ -310,7 +348,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             float2 sum2 = make_float2(0.f, 0.f);
-            const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
+            const float2 scale2 = make_float2(sl2, sl2), minus_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t packed[32];
@@ -330,6 +368,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[i]));
         }
+        // the sink: one more term of score 0 (with shares of the keys, the kernel that joins them adds it)
+        if (kSink && extras.sink && n_splits == 1) l += m_ref == -INFINITY ? 1.f : ex2(-m_ref);
         if (ok && n_blocks > 0) {
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&o_full[i]), 0))) {
                 if (lane == 0) fail(ERR_O_FULL);
@@ -767,9 +807,11 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
 }  // namespace fa5
 
 namespace fa5 {
-// out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M), M = max_s m_s, over the shares s of the keys.
+// out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M), M = max_s m_s, over the shares s of the keys;
+// with ``sink`` the denominator has one more term 2^(0 - M).
 __global__ void combine_key_shares_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                          bf16* __restrict__ out, int n_tokens, int n_heads, int D, int n_splits) {
+                                          bf16* __restrict__ out, int n_tokens, int n_heads, int D, int n_splits,
+                                          int sink) {
     const int64_t th = (int64_t)blockIdx.x * n_heads + blockIdx.y;
     const int64_t stride = (int64_t)n_tokens * n_heads;
     float mx = -INFINITY;
@@ -779,6 +821,7 @@ __global__ void combine_key_shares_kernel(const float* __restrict__ part_o, cons
         const float m = part_ml[2 * (s * stride + th)];
         if (m != -INFINITY) denom += part_ml[2 * (s * stride + th) + 1] * exp2f(m - mx);
     }
+    if (sink) denom += mx == -INFINITY ? 1.f : exp2f(-mx);
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float acc = 0.f;
@@ -790,27 +833,27 @@ __global__ void combine_key_shares_kernel(const float* __restrict__ part_o, cons
     }
 }
 
-template <int D>
+template <int D, bool kSink = false>
 static int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_row,
                   int n_tiles, const int* cu_q, const int* kv_len, const int* slots, const int* page_table, int max_pages,
                   int n_tokens, int n_pages, int n_heads, int n_kv, float scale, float* scratch, int n_splits,
-                  cudaStream_t stream, int v_shift = 0) {
+                  cudaStream_t stream, int v_shift = 0, SinkExtras extras = SinkExtras{0, 0.f, 0.f, 0}) {
     CUtensorMap map_q, map_k, map_v;
     if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * D, (uint64_t)n_heads * D * 2, 64, kTileRows) ||
         !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, D, D * 2, 64, kPageTokens) ||
         !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * D, kPageTokens, kPageTokens * 2, 64, D))
         return CPM_BAD_ARGUMENT;
-    auto kern = prefill_attention_tcgen05_kernel<D>;
+    auto kern = prefill_attention_tcgen05_kernel<D, kSink>;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, Sizes<D>::kSmemBytes, configured)) return st;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (int64_t)n_splits * n_tokens * n_heads * D : nullptr;
     kern<<<dim3(n_heads / 2, n_tiles, n_splits), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out,
         tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f,
-        part_o, part_ml, n_splits, n_tokens, v_shift);
+        part_o, part_ml, n_splits, n_tokens, v_shift, extras);
     if (n_splits > 1)
         combine_key_shares_kernel<<<dim3(n_tokens, n_heads), D / 2, 0, stream>>>(part_o, part_ml, (bf16*)out, n_tokens, n_heads,
-                                                                               D, n_splits);
+                                                                               D, n_splits, kSink ? extras.sink : 0);
     return launch_status();
 }
 }  // namespace fa5
@@ -854,6 +897,27 @@ CPM_API int cpm_prefill_attention_tcgen05_vshift(const void* q, const void* k_ca
                                 n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, v_shift);
     return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
                            n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, v_shift);
+}
+
+// Sink window attention of prompt tokens on the same kernel: keys 0 <= i - j < window (0: all), scores capped as
+// cap * tanh(s / cap) when cap > 0, one added to the softmax's denominator when sink != 0.  Sizes and scratch as above.
+CPM_API int cpm_sink_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
+                                       const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                       int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale, int window,
+                                       float cap, int sink, float* scratch, int n_splits, cudaStream_t stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !scratch) || n_tokens > 65535 * 1024) return CPM_BAD_ARGUMENT;
+    if ((d != 128 && d != 64) || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
+        window < 0 || cap < 0.f || !(scale > 0.f) ||
+        ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return CPM_BAD_ARGUMENT;
+    const fa5::SinkExtras extras{window, cap * 1.4426950408889634f, cap > 0.f ? scale / cap : 0.f, sink};
+    if (d == 128)
+        return fa5::launch<128, true>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table,
+                                      max_pages, n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, 0, extras);
+    return fa5::launch<64, true>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table,
+                                 max_pages, n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, 0, extras);
 }
 
 // Block-list attention of prompt tokens on the tensor cores (see listed_attention_tcgen05_kernel): q, out [tokens, heads,

@@ -415,6 +415,73 @@ def test_sink_window_attention_batches_unequal_sequences(dtype):
         _close(torch.cat(got[i]), want[i][:done[i]], dtype)
 
 
+@pytest.mark.parametrize("shares", [None, 3])
+@pytest.mark.parametrize("H,G,d,window,cap,sink", [(4, 2, 128, 200, 20.0, True), (2, 1, 64, 1100, 0.0, True), (4, 1, 128, None, 30.0, False),
+                                                   (2, 1, 128, 128, 0.0, True), (2, 1, 128, 1, 10.0, True), (6, 3, 64, 129, 15.0, True)])
+def test_prompt_portions_on_the_tcgen05_kernel(H, G, d, window, cap, sink, shares):
+    """Prompt portions of two sequences of unequal lengths on the 128-row tiles of the tcgen05 kernel: windows shorter
+    than, equal to and longer than a key step of 128, no window, with and without cap and sink, the keys of a tile in
+    one block and shared among three.  Scores tower at the last key a window holds and at the first it has dropped
+    (see ``_towers``); the second sequence ends inside the first tile."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(H + d)
+    lens, scale = [1300, 200], 0.25
+    data = [[torch.randn(n, H, d, generator=g) * 0.5, torch.randn(n, G, d, generator=g) * 0.5, torch.randn(n, G, d, generator=g)]
+            for n in lens]
+    for (q, k, v), n in zip(data, lens):
+        seen, unseen = _towers(n, window)
+        for qi, kj in seen:
+            q[qi, :, 1] = 9.0
+            k[kj, :, 1] = 9.0
+        marked = {qi for qi, _ in seen} | {kj for _, kj in seen}
+        for qi, kj in unseen:
+            if kj not in marked:
+                k[kj, :, 1] = 30.0
+        for qi, _ in seen:
+            if qi + 1 < n and qi + 1 not in marked:
+                k[qi + 1, :, 1] = 30.0
+    rnd = lambda t: t.bfloat16().double()
+    want = [plain.window_attention_core(rnd(q), rnd(k), rnd(v), scale, cap, window, sink).reshape(n, H * d) for (q, k, v), n in zip(data, lens)]
+    cache = Cache([CacheNeeds(kv_heads=G, head_dim=d, window=window)], max_tokens=64 * 30, dtype=torch.bfloat16, device="cuda:0",
+                  n_slots=4)
+    cache.open_sequence()
+    slots = [cache.open_sequence() for _ in lens]
+    lane = cache.lane(0)
+    calls = []
+    inner = ops.sink_attention_tcgen05
+    ops.sink_attention_tcgen05 = lambda *a, **kw: (calls.append(1), inner(*a, **kw))[1]
+    if shares:
+        ops.prefill_key_shares = lambda *a, **kw: shares
+    done, got = [0, 0], [[], []]
+    for step in ([640, 200], [129, 0], [531, 0]):
+        live = [i for i in range(2) if step[i] > 0]
+        for i in live:
+            cache.reserve(slots[i], done[i] + step[i])
+        cache.sync()
+        ctx = _ctx([step[i] for i in live], [done[i] for i in live], [slots[i] for i in live])
+        proj = torch.cat([torch.cat([t[done[i]:done[i] + step[i]].reshape(step[i], -1) for t in data[i]], dim=1) for i in live])
+        qr = ops.qk_prepare_store(ctx, proj.bfloat16().float().cuda().contiguous(), lane, H, G, d, d, (None, None, None), None, 0,
+                                  False, 0.0)
+        o = ops.sink_attention(ctx, qr, lane, G, d, scale, window or 0, cap, sink)
+        at = 0
+        for i in live:
+            got[i].append(o[at:at + step[i]])
+            at += step[i]
+            done[i] += step[i]
+    ops.raise_on_kernel_error()
+    assert len(calls) == (3 if d == 128 else 1)          # head size 64 goes there from 1,024 keys on
+    for i in range(2):
+        full = torch.cat(got[i])
+        _close(full, want[i], "bfloat16")
+        seen, _ = _towers(lens[i], window)
+        for qi in sorted({qi for qi, _ in seen}):
+            _close(full[qi], want[i][qi], "bfloat16")
+
+
 @pytest.mark.parametrize("H,G,d,dv,window,sink", [(6, 2, 64, 64, 700, True), (4, 1, 128, 32, None, True), (20, 1, 32, 128, 1000, False)])
 def test_single_tokens_whose_keys_are_shared_among_blocks(H, G, d, dv, window, sink):
     """Two sequences of unequal lengths bring one token each; the keys of a token are divided among 1, 3 and 16 blocks
