@@ -422,7 +422,8 @@ def test_prompt_portions_on_the_tcgen05_kernel(H, G, d, window, cap, sink, share
     """Prompt portions of two sequences of unequal lengths on the 128-row tiles of the tcgen05 kernel: windows shorter
     than, equal to and longer than a key step of 128, no window, with and without cap and sink, the keys of a tile in
     one block and shared among three.  Scores tower at the last key a window holds and at the first it has dropped
-    (see ``_towers``); the second sequence ends inside the first tile."""
+    (see ``_towers``); the second sequence ends inside the first tile; pages that a window has left are given back after
+    every step, so that a tile's first key step begins in a page that now holds later keys."""
     from cpmcu_b200.cache import Cache
     from cpmcu_b200.ops.ops import Ops
     from cpmcu_b200.parts.base import CacheNeeds
@@ -472,6 +473,7 @@ def test_prompt_portions_on_the_tcgen05_kernel(H, G, d, window, cap, sink, share
             got[i].append(o[at:at + step[i]])
             at += step[i]
             done[i] += step[i]
+            cache.set_length(slots[i], done[i])          # pages behind the window go back and are taken again below
     ops.raise_on_kernel_error()
     assert len(calls) == (3 if d == 128 else 1)          # head size 64 goes there from 1,024 keys on
     for i in range(2):
