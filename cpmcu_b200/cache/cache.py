@@ -10,7 +10,8 @@ page is its transpose [kv_head][head_dim][token_in_page].  Pages and slots go ba
 a sequence ends and are used again as they are: only a slot's state is cleared, its
 pages never are.  A group whose lanes look at a window of keys gives a sequence's pages
 back as soon as every key in them has fallen out of the window of all later queries,
-so what such a group holds per sequence is bounded by the window and the step size.
+so what such a group holds per sequence is bounded by the window and the step size;
+the pages of the first tokens that such a window keeps (``CacheNeeds.keep_first``) stay.
 
 The reference keeps one sequence in one contiguous buffer per layer
 (src/model/kvcache.cuh:7-26) and its per-sequence counters in host-side fields of each
@@ -50,6 +51,7 @@ class CacheGroup:
         self.pages = FreeList(n_pages, "page")
         self.pages_of_slot: Dict[int, List[int]] = {}     # by logical page; RELEASED where the window has moved on
         self.first_live: Dict[int, int] = {}              # slot -> first logical page still held
+        self.kept_pages = pages_for(needs.keep_first) if needs.window and needs.keep_first else 0
         self.page_table = make("state", (n_slots, max_pages_per_seq), torch.int32, True)
         self._dirty: Dict[int, int] = {}      # slot -> first table column not yet on the device
         n = len(lanes)
@@ -107,7 +109,8 @@ class CacheGroup:
         if not pages:
             return 0
         dead = min(max(0, length - window + 1) // PAGE_TOKENS, len(pages))
-        first = self.first_live.get(slot, 0)
+        # the pages that hold kept first tokens are never given back: the stretch that moves begins behind them
+        first = max(self.first_live.get(slot, 0), self.kept_pages)
         if dead <= first:
             return 0
         self.pages.give_back(pages[first:dead])
@@ -121,10 +124,10 @@ class CacheGroup:
         write can reach a copy that is still queued)."""
         for slot, first in self._dirty.items():
             pages = self.pages_of_slot[slot]
-            first = max(first, self.first_live.get(slot, 0))
+            first = max(first, self.first_live.get(slot, 0)) if first >= self.kept_pages else first
             if first >= len(pages):
                 continue
-            row = torch.tensor(pages[first:], dtype=torch.int32)
+            row = torch.tensor([max(p, 0) for p in pages[first:]], dtype=torch.int32)      # a released page: no kernel follows it
             self.page_table[slot, first:len(pages)].copy_(row)
         self._dirty.clear()
 
@@ -195,7 +198,7 @@ class Cache:
             group_pages = n_pages
             if needs.window and max_step_tokens:
                 # a sequence holds at most the pages its window and one step's tokens touch
-                per_slot = pages_for(needs.window + int(max_step_tokens)) + 1
+                per_slot = pages_for(needs.window + int(max_step_tokens)) + 1 + pages_for(needs.keep_first)
                 group_pages = min(n_pages, self.n_slots * per_slot)
             group = CacheGroup(needs, lane_ids, group_pages, self.n_slots, self.max_pages_per_seq, dtype, self.device, make)
             self.groups.append(group)
@@ -245,7 +248,7 @@ class Cache:
                     raise HandleError(f"slot {slot} is not open")
                 extra = pages_for(new_length) - len(g.pages_of_slot.get(slot, []))
                 if g.needs.window:
-                    peak = pages_for(g.needs.window + int(step_tokens)) + 1      # most pages a sequence holds at once
+                    peak = pages_for(g.needs.window + int(step_tokens)) + 1 + g.kept_pages      # most pages a sequence holds at once
                     extra = min(extra, peak - g.pages_held(slot))
                 need += max(0, extra)
             if need > g.pages.n_free:

@@ -3,6 +3,7 @@ from .minicpm import MiniCPMConfig, RopeScaling, SparseConfig
 from .reravik import ReravikConfig
 from .mufevik import MufevikConfig
 from .kipizen import KipizenConfig
+from .lukelorn import LukelornConfig
 
 __all__ = ["ConfigError", "FieldReader", "architecture_name", "read_config_json", "MiniCPMConfig", "RopeScaling",
-           "SparseConfig", "ReravikConfig", "MufevikConfig", "KipizenConfig"]
+           "SparseConfig", "ReravikConfig", "MufevikConfig", "KipizenConfig", "LukelornConfig"]

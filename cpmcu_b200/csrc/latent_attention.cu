@@ -7,8 +7,10 @@
 // the attention runs on the cached latents themselves: one shared "key = value" row per token for all heads.
 // A query at position p sees the keys j with 0 <= p - j < window (window 0: every j <= p).
 //
-//   latent_norm_store   RMS-norms the two parts of the fused down projection [tokens, q_rank + rank] (fp32):
-//                       the query latent goes on as an activation, the key-value latent into the cache pages
+//   latent_norm_store   RMS-norms the two parts of the fused down projection [tokens, q_rank + rank (+ rot_dim)] (fp32):
+//                       the query latent goes on as an activation, the key-value latent into the cache pages, followed
+//                       there by the rotated key part that all heads share (when the design has one)
+//   rotate_heads        turns a range of channels of every head by the token's position
 //   head_project        out[t, h, :] = in[t, h, :] @ w[h]   (w [heads][k][n]; fp32 accumulation), the per-head
 //                       maps Uk^T (queries into the latent space) and Uv (weighted latents into values)
 //   latent_attention    softmax attention of [tokens, heads, rank] fp32 queries over the latent pages (rank up to 1,024); scores,
@@ -19,16 +21,21 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
+// proj rows (fp32, ``stride`` floats) begin [q_rank | rank | rot_dim]: the first two parts are RMS-normed; the third (rot_dim
+// may be 0) is one key part shared by all heads that is turned by the token's position, pairs (c, c + rot_dim/2) or with
+// ``adjacent`` (2c, 2c + 1), angle position * inv_freq[c], and not normed.  The cache row of the token is [rank | rot_dim].
 template <typename T>
-__global__ void latent_norm_store_kernel(const float* __restrict__ proj, const float* __restrict__ wq, const float* __restrict__ wkv,
-                                         T* __restrict__ cq, T* __restrict__ cache, const int* __restrict__ positions,
-                                         const int* __restrict__ token_seq, const int* __restrict__ slots,
-                                         const int* __restrict__ page_table, int max_pages, int q_rank, int rank, float eps) {
+__global__ void latent_norm_store_kernel(const float* __restrict__ proj, int64_t stride, const float* __restrict__ wq,
+                                         const float* __restrict__ wkv, T* __restrict__ cq, T* __restrict__ cache,
+                                         const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                                         int q_rank, int rank, int rot_dim, const float* __restrict__ inv_freq, int adjacent,
+                                         float eps) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const float* row = proj + (int64_t)t * (q_rank + rank);
+    const float* row = proj + (int64_t)t * stride;
     float s = 0.f;
     for (int c = threadIdx.x; c < q_rank; c += blockDim.x) s = fmaf(row[c], row[c], s);
     float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)q_rank + eps);
@@ -41,22 +48,81 @@ __global__ void latent_norm_store_kernel(const float* __restrict__ proj, const f
     const int p = positions[t];
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
     const int page = CPM_PAGE(pages, p / kPageTokens, max_pages);
-    T* dst = cache + page_row_offset(page, 0, p % kPageTokens, 1, rank);
+    T* dst = cache + page_row_offset(page, 0, p % kPageTokens, 1, rank + rot_dim);
     for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = from_f32<T>(row[c] * r * wkv[c]);
+    row += rank;
+    dst += rank;
+    const int half = rot_dim >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int a = adjacent ? 2 * i : i, b = adjacent ? 2 * i + 1 : i + half;
+        float sn = 0.f, cs = 1.f;
+        if (inv_freq != nullptr) sincosf((float)p * inv_freq[i], &sn, &cs);
+        const float u = row[a], v = row[b];
+        dst[a] = from_f32<T>(u * cs - v * sn);
+        dst[b] = from_f32<T>(v * cs + u * sn);
+    }
 }
 
-CPM_API int cpm_latent_norm_store(const float* proj, const float* wq, const float* wkv, void* cq, void* cache,
+CPM_API int cpm_latent_norm_store(const float* proj, int64_t stride, const float* wq, const float* wkv, void* cq, void* cache,
                                   const int* positions, const int* token_seq, const int* slots, const int* page_table,
-                                  int max_pages, int n_tokens, int q_rank, int rank, float eps, int dtype, cudaStream_t stream) {
+                                  int max_pages, int n_tokens, int q_rank, int rank, int rot_dim, const float* inv_freq,
+                                  int adjacent, float eps, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (q_rank <= 0 || rank <= 0) return CPM_BAD_ARGUMENT;
+    if (q_rank <= 0 || rank <= 0 || rot_dim < 0 || (rot_dim & 1) || stride < q_rank + rank + rot_dim) return CPM_BAD_ARGUMENT;
     const int threads = (q_rank + rank) >= 1024 ? 256 : 128;
     if (dtype == CPM_BF16)
-        cpm_launch(kLaunchRope, latent_norm_store_kernel<bf16>, n_tokens, threads, 0, stream, proj, wq, wkv, (bf16*)cq, (bf16*)cache,
-                   positions, token_seq, slots, page_table, max_pages, q_rank, rank, eps);
+        cpm_launch(kLaunchRope, latent_norm_store_kernel<bf16>, n_tokens, threads, 0, stream, proj, stride, wq, wkv, (bf16*)cq,
+                   (bf16*)cache, positions, token_seq, slots, page_table, max_pages, q_rank, rank, rot_dim, inv_freq, adjacent, eps);
     else
-        cpm_launch(kLaunchRope, latent_norm_store_kernel<float>, n_tokens, threads, 0, stream, proj, wq, wkv, (float*)cq,
-                   (float*)cache, positions, token_seq, slots, page_table, max_pages, q_rank, rank, eps);
+        cpm_launch(kLaunchRope, latent_norm_store_kernel<float>, n_tokens, threads, 0, stream, proj, stride, wq, wkv, (float*)cq,
+                   (float*)cache, positions, token_seq, slots, page_table, max_pages, q_rank, rank, rot_dim, inv_freq, adjacent,
+                   eps);
+    return launch_status();
+}
+
+// out[t][h][:] = in[t][h][:] (fp32 in, storage type out; heads of ``dh`` channels) with the channels [first, first + rot_dim)
+// of every head turned by the token's position: pairs (c, c + rot_dim/2) or with ``adjacent`` (2c, 2c + 1) counted from
+// ``first``, angle position * inv_freq[c].  One thread per pair or per channel outside the turned part.
+template <typename T>
+__global__ void rotate_heads_kernel(const float* __restrict__ in, T* __restrict__ out, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int64_t n_units, int n_heads, int dh, int first,
+                                    int rot_dim, int adjacent) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_units) return;
+    const int per_head = dh - rot_dim / 2;                  // plain channels and pairs of a head
+    const int64_t th = i / per_head;
+    const int u = (int)(i % per_head);
+    const int64_t base = th * dh;
+    const int plain = dh - rot_dim;
+    if (u < plain) {
+        const int c = u < first ? u : u + rot_dim;
+        out[base + c] = from_f32<T>(in[base + c]);
+        return;
+    }
+    const int k = u - plain, half = rot_dim >> 1;
+    const int a = first + (adjacent ? 2 * k : k), b = first + (adjacent ? 2 * k + 1 : k + half);
+    float sn, cs;
+    sincosf((float)positions[th / n_heads] * inv_freq[k], &sn, &cs);
+    const float x = in[base + a], y = in[base + b];
+    out[base + a] = from_f32<T>(x * cs - y * sn);
+    out[base + b] = from_f32<T>(y * cs + x * sn);
+}
+
+CPM_API int cpm_rotate_heads(const float* in, void* out, const int* positions, const float* inv_freq, int n_tokens, int n_heads,
+                             int dh, int first, int rot_dim, int adjacent, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_heads < 1 || dh < 1 || first < 0 || rot_dim < 0 || (rot_dim & 1) || first + rot_dim > dh || (rot_dim && !inv_freq))
+        return CPM_BAD_ARGUMENT;
+    const int64_t n = (int64_t)n_tokens * n_heads * (dh - rot_dim / 2);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == CPM_BF16)
+        cpm_launch(kLaunchRope, rotate_heads_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, in, (bf16*)out, positions, inv_freq, n,
+                   n_heads, dh, first, rot_dim, adjacent);
+    else
+        cpm_launch(kLaunchRope, rotate_heads_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float*)out, positions, inv_freq,
+                   n, n_heads, dh, first, rot_dim, adjacent);
     return launch_status();
 }
 

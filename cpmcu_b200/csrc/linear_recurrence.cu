@@ -271,7 +271,7 @@ CPM_API int cpm_linear_recurrence(const float* q, const float* k, int64_t qk_str
 // step's first token come from conv_state [slots, K-1, C] (oldest first).  q and k heads are then scaled to unit
 // length, x / sqrt(sum x^2 + unit_eps).  One warp per (token, head of q, k or v).  For value head h the first lane
 // also forms beta = sigmoid(b_raw) and the decay exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h])) from the
-// columns ``b_col + h`` and ``a_col + h`` of the row.
+// columns ``b_col + h`` and ``a_col + h`` of the row (no decay when ``decay`` is null: a caller that forms its own).
 // ---------------------------------------------------------------------------
 constexpr int kConvMaxPerLane = 8;      // head sizes up to 256
 constexpr int kConvMaxTaps = 8;
@@ -328,7 +328,7 @@ __global__ void conv_prepare_kernel(const float* __restrict__ proj, int64_t stri
         const int h = unit - 2 * qk_heads;
         const float* row = proj + (int64_t)t * stride;
         beta[(int64_t)t * heads + h] = sigmoid_acc(row[b_col + h]);
-        decay[(int64_t)t * heads + h] = expf(-expf(a_log[h]) * softplus_acc(row[a_col + h] + dt_bias[h]));
+        if (decay != nullptr) decay[(int64_t)t * heads + h] = expf(-expf(a_log[h]) * softplus_acc(row[a_col + h] + dt_bias[h]));
     }
 }
 
@@ -381,6 +381,28 @@ CPM_API int cpm_conv_prepare(const float* proj, int64_t stride, const float* tap
         cpm_launch(kLaunchOther, conv_state_update_kernel, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, proj, stride,
                    conv_state, positions, cu_q, slots, C, K);
     }
+    return launch_status();
+}
+
+// A decay per head and key channel, in place on fp32 rows [heads * d]:
+//   z <- exp(-exp(a_log[h]) * softplus(z + dt_bias[h * d + c]))
+__global__ void channel_decay_kernel(float* __restrict__ z, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                     int64_t n, int width, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int c = (int)(i % width);
+    z[i] = expf(-expf(a_log[c / d]) * softplus_acc(z[i] + dt_bias[c]));
+}
+
+CPM_API int cpm_channel_decay(float* z, const float* a_log, const float* dt_bias, int n_tokens, int heads, int d,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (heads < 1 || d < 1) return CPM_BAD_ARGUMENT;
+    const int64_t n = (int64_t)n_tokens * heads * d;
+    cpm_launch(kLaunchOther, channel_decay_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, z, a_log, dt_bias, n,
+               heads * d, d);
     return launch_status();
 }
 

@@ -4,14 +4,17 @@
 // ``n_groups`` equal groups of neighbours, a group's score is its largest choice score, and only experts of the
 // ``keep`` best groups can be chosen (the others count as minus infinity); the ``top`` largest choice scores are
 // chosen, and their weights are the plain scores s, not renormalised.  Ties go to the lower index.
-// A second rule (``top_first``): the choice scores are the logits plus a bias, the ``top`` largest are chosen, and
-// their weights are the softmax over the chosen logits only.
+// A second rule (``top_first`` 1): the choice scores are the logits plus a bias, the ``top`` largest are chosen, and
+// their weights are the softmax over the chosen logits only.  A third (``top_first`` 2): the scores are the sigmoids of
+// the logits, the ``top`` largest are chosen, and their weights are those scores, not renormalised.
 //
 // Products: the (token, choice) pairs are grouped by expert (counts, offsets, a list of pairs in expert order),
 // and tiles of 32 pairs of one expert times 64 output features run as blocks of one launch, whose grid is an upper
 // bound on the tile count (blocks beyond the last tile leave at once), so nothing is read back on the host:
-//   gated:  H[r] = silu(x[token(r)] Wg_e^T) * (x[token(r)] Wu_e^T)     r: place in expert order
-//   down:   Y[pair(r)] = H[r] Wd_e^T
+//   gated (mode 1):  H[r] = silu(x[token(r)] Wg_e^T) * (x[token(r)] Wu_e^T)     r: place in expert order
+//   up (mode 2):     H[r] = relu(s[pair(r)] * (x[token(r)] Wu_e^T))^2           s: a number per pair (null: 1), which is
+//                    the expert of the input times s, since the product is linear in its input
+//   down (mode 0):   Y[pair(r)] = H[r] Wd_e^T
 // and a last kernel adds up a token's pairs with their weights and the shared expert's output times its gate.
 // Accumulation is fp32: on the CUDA cores for 32-bit storage (and where K is no multiple of 8), on the tensor cores for bf16.
 #include "common.cuh"
@@ -45,6 +48,28 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const
     float* c = s + E;                                                 // choice scores
     float* gs = c + E;                                                // group scores
     const float* z = logits + (int64_t)t * ld;
+    if (top_first == 2) {
+        // scores: sigmoid of the logits; the ``top`` largest are chosen and their scores are the weights as they are
+        for (int e = lane; e < E; e += 32) c[e] = 1.0f / (1.0f + expf(-(z[e] + (bias ? bias[e] : 0.f))));
+        __syncwarp();
+        for (int r = 0; r < top; ++r) {
+            ArgMax a{-INFINITY, 0x7fffffff};
+            for (int e = lane; e < E; e += 32) {
+                const float v = c[e];
+                if (!isnan(v)) a = better(a, ArgMax{v, e});
+            }
+            a = warp_argmax(a);
+            const int e = a.i < E ? a.i : 0;
+            if (lane == 0) {
+                chosen[(int64_t)t * top + r] = e;
+                weights[(int64_t)t * top + r] = a.v;
+                c[e] = NAN;                               // taken
+            }
+            __syncwarp();
+        }
+        if (gate_col >= 0 && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-z[gate_col]));
+        return;
+    }
     if (top_first) {
         // choice scores: logits + bias; weights: softmax over the chosen scores (the largest is the first chosen)
         for (int e = lane; e < E; e += 32) c[e] = z[e] + (bias ? bias[e] : 0.f);
@@ -161,10 +186,12 @@ constexpr int kTileM = 32, kTileN = 64, kTileK = 32;
 // C[row_out(r)][n] = sum_k A[row_in(r)][k] * B_e[n][k] for the places r of expert e, tile by tile.
 // GATED: A rows are tokens (pair / top), two weight stacks (gate, up) and the result is silu(gate) * up, written at
 // row r.  Otherwise A rows are the places r themselves and the result goes to row pair(r).
-template <typename T, bool GATED>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_tile_kernel(const T* __restrict__ A, const T* __restrict__ B0, const T* __restrict__ B1, T* __restrict__ C,
-                const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K) {
+                const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K,
+                const float* __restrict__ in_scale) {
+    constexpr bool GATED = MODE == 1, BY_TOKEN = MODE != 0;
     __shared__ float As[kTileM][kTileK + 1], Bs0[kTileN][kTileK + 1], Bs1[GATED ? kTileN : 1][kTileK + 1];
     __shared__ int s_tile[3];
     pdl_launch_dependents();
@@ -194,7 +221,7 @@ moe_tile_kernel(const T* __restrict__ A, const T* __restrict__ B0, const T* __re
             const int r = i / kTileK, kk = i % kTileK;
             float v = 0.f;
             if (r < rows && k0 + kk < K) {
-                const int64_t src = GATED ? (int64_t)(order[r0 + r] / top) : (int64_t)(r0 + r);
+                const int64_t src = BY_TOKEN ? (int64_t)(order[r0 + r] / top) : (int64_t)(r0 + r);
                 v = to_f32(A[src * K + k0 + kk]);
             }
             As[r][kk] = v;
@@ -227,13 +254,15 @@ moe_tile_kernel(const T* __restrict__ A, const T* __restrict__ B0, const T* __re
     for (int i = 0; i < 2; ++i) {
         const int r = ty * 2 + i;
         if (r >= rows) continue;
-        const int64_t dst = GATED ? (int64_t)(r0 + r) : (int64_t)order[r0 + r];
+        const int64_t dst = BY_TOKEN ? (int64_t)(r0 + r) : (int64_t)order[r0 + r];
+        const float sc = (MODE == 2 && in_scale != nullptr) ? in_scale[order[r0 + r]] : 1.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc0[i][j];
             if (GATED) v = v / (1.0f + expf(-v)) * acc1[i][j];
+            if (MODE == 2) { v = fmaxf(v * sc, 0.f); v *= v; }
             C[dst * N + n] = from_f32<T>(v);
         }
     }
@@ -265,10 +294,12 @@ __device__ __forceinline__ void cp_async_16(bf16* smem_dst, const bf16* gmem_src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
 }
 
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, bf16* __restrict__ C,
-                    const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K) {
+                    const int* __restrict__ offsets, const int* __restrict__ order, int E, int top, int N, int K,
+                    const float* __restrict__ in_scale) {
+    constexpr bool GATED = MODE == 1, BY_TOKEN = MODE != 0;
     __shared__ __align__(16) bf16 As[2][kMmaM][kMmaPad], Bs0[2][kMmaN][kMmaPad], Bs1[GATED ? 2 : 1][GATED ? kMmaN : 1][kMmaPad];
     __shared__ int s_tile[3];
     __shared__ int s_rows[kMmaM];
@@ -304,7 +335,7 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
         const int r = (threadIdx.x + 256 * i) >> 2;
         const int pair = s_rows[r];
         a_ok[i] = pair >= 0;
-        a_src[i] = A + (int64_t)(a_ok[i] ? (GATED ? pair / top : r0 + r) : 0) * K;
+        a_src[i] = A + (int64_t)(a_ok[i] ? (BY_TOKEN ? pair / top : r0 + r) : 0) * K;
     }
     const int b_row = threadIdx.x >> 2, piece = 8 * (threadIdx.x & 3);
     const bool b_ok = n0 + b_row < N;
@@ -352,7 +383,8 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
         for (int half = 0; half < 2; ++half) {
             const int r = wm * 32 + mt * 16 + g + 8 * half;
             if (r >= rows) continue;
-            const int64_t dst = GATED ? (int64_t)(r0 + r) : (int64_t)s_rows[r];
+            const int64_t dst = BY_TOKEN ? (int64_t)(r0 + r) : (int64_t)s_rows[r];
+            const float sc = (MODE == 2 && in_scale != nullptr) ? in_scale[s_rows[r]] : 1.f;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -361,6 +393,7 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
                     if (n >= N) continue;
                     float v = acc0[mt][nt][2 * half + q];
                     if (GATED) v = v / (1.0f + expf(-v)) * acc1[mt][nt][2 * half + q];
+                    if (MODE == 2) { v = fmaxf(v * sc, 0.f); v *= v; }
                     C[dst * N + n] = __float2bfloat16_rn(v);
                 }
         }
@@ -371,17 +404,19 @@ moe_tile_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, con
 // in 16-byte pieces and the sums meet by shuffles.  No grouping by expert is needed: H and Y are indexed by pair.
 constexpr int kGemvFeatures = 32;
 
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_pair_gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, bf16* __restrict__ C,
-                     const int* __restrict__ chosen, int top, int N, int K) {
+                     const int* __restrict__ chosen, int top, int N, int K, const float* __restrict__ in_scale) {
+    constexpr bool GATED = MODE == 1, BY_TOKEN = MODE != 0;
     extern __shared__ float gemv_x[];                          // the pair's input row, fp32
     pdl_launch_dependents();
     const int pair = blockIdx.x, n0 = blockIdx.y * kGemvFeatures;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
     const int e = chosen[pair];
-    const bf16* x = A + (int64_t)(GATED ? pair / top : pair) * K;
+    const bf16* x = A + (int64_t)(BY_TOKEN ? pair / top : pair) * K;
+    const float sc = (MODE == 2 && in_scale != nullptr) ? in_scale[pair] : 1.f;
     for (int i = threadIdx.x; i < K; i += blockDim.x) gemv_x[i] = __bfloat162float(x[i]);
     __syncthreads();
     const bf16* W0 = B0 + (int64_t)e * N * K;
@@ -412,30 +447,31 @@ moe_pair_gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, co
         }
         s0 = warp_sum(s0);
         if (GATED) s1 = warp_sum(s1);
+        if (MODE == 2) { s0 = fmaxf(s0 * sc, 0.f); s0 *= s0; }
         if (lane == 0) C[(int64_t)pair * N + n] = __float2bfloat16_rn(GATED ? s0 / (1.0f + expf(-s0)) * s1 : s0);
     }
 }
 
 // The same two products for few pairs, by pair: gated: C = H [pairs, N] by pair from x [tokens, K]; else C = Y [pairs, N]
 // from H [pairs, K] by pair.  bf16, K a multiple of 8.
+// mode 1: gated; 2: one stack, relu(in_scale[pair] * product)^2, from x by pair; 0: the down product.
 CPM_API int cpm_moe_pair_product(const void* A, const void* B0, const void* B1, void* C, const int* chosen, int n_pairs, int top,
-                                 int N, int K, int gated, cudaStream_t stream) {
+                                 int N, int K, int mode, const float* in_scale, cudaStream_t stream) {
     if (n_pairs <= 0) return CPM_OK;
     if (top < 1 || N < 1 || K < 8 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)B0 & 15) || ((uintptr_t)B1 & 15) ||
         (size_t)K * sizeof(float) > 48 * 1024)
         return CPM_BAD_ARGUMENT;
     const dim3 grid(n_pairs, (N + kGemvFeatures - 1) / kGemvFeatures);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
-    if (gated)
-        cpm_launch(kLaunchProduct, moe_pair_gemv_kernel<true>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const bf16*)A,
-                   (const bf16*)B0, (const bf16*)B1, (bf16*)C, chosen, top, N, K);
-    else
-        cpm_launch(kLaunchProduct, moe_pair_gemv_kernel<false>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const bf16*)A,
-                   (const bf16*)B0, (const bf16*)B1, (bf16*)C, chosen, top, N, K);
+    if (mode < 0 || mode > 2) return CPM_BAD_ARGUMENT;
+#define CPM_GEMV(M) cpm_launch(kLaunchProduct, moe_pair_gemv_kernel<M>, grid, dim3(256), (size_t)K * sizeof(float), stream,      \
+                               (const bf16*)A, (const bf16*)B0, (const bf16*)B1, (bf16*)C, chosen, top, N, K, in_scale)
+    if (mode == 1) CPM_GEMV(1); else if (mode == 2) CPM_GEMV(2); else CPM_GEMV(0);
+#undef CPM_GEMV
     return launch_status();
 }
 
-// out[t] = sum_k weights[t][k] * Y[t * top + k] + gate[t] * shared[t]
+// out[t] = sum_k weights[t][k] * Y[t * top + k] + gate[t] * shared[t]   (weights null: all 1)
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ Y, const float* __restrict__ weights, const T* __restrict__ shared,
                                    const float* __restrict__ gate, T* __restrict__ out, int top, int W) {
@@ -444,7 +480,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ Y, const float* __restr
     const int64_t t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) v = fmaf(weights[t * top + k], to_f32(Y[(t * top + k) * W + c]), v);
+        for (int k = 0; k < top; ++k) v = fmaf(weights ? weights[t * top + k] : 1.f, to_f32(Y[(t * top + k) * W + c]), v);
         if (shared) v = fmaf(gate ? gate[t] : 1.f, to_f32(shared[t * W + c]), v);
         out[t * W + c] = from_f32<T>(v);
     }
@@ -461,7 +497,7 @@ CPM_API int cpm_moe_route(const float* logits, int ld, const float* correction, 
                           int gate_col, int n_tokens, int E, int top, int n_groups, int keep, const float* bias, int top_first,
                           cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (!top_first && !correction) return CPM_BAD_ARGUMENT;
+    if (top_first < 0 || top_first > 2 || (!top_first && !correction)) return CPM_BAD_ARGUMENT;
     if (E < 1 || E > 32 * kRouteMaxPerLane || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups ||
         top > keep * (E / n_groups))
         return CPM_BAD_ARGUMENT;
@@ -480,30 +516,30 @@ CPM_API int cpm_moe_group(const int* chosen, int n_pairs, int E, int* offsets, i
     return launch_status();
 }
 
-// gated != 0: A = x [tokens, K], B0 = gate stack [E, N, K], B1 = up stack, C = H [pairs, N] in expert order.
-// gated == 0: A = H [pairs, K] in expert order, B0 = down stack [E, N, K], C = Y [pairs, N] by pair.
+// mode 1: A = x [tokens, K], B0 = gate stack [E, N, K], B1 = up stack, C = H [pairs, N] in expert order.
+// mode 2: A = x, B0 = up stack, C = H = relu(in_scale[pair] * product)^2 in expert order (in_scale null: 1).
+// mode 0: A = H [pairs, K] in expert order, B0 = down stack [E, N, K], C = Y [pairs, N] by pair.
 CPM_API int cpm_moe_expert_product(const void* A, const void* B0, const void* B1, void* C, const int* offsets, const int* order,
-                                   int n_pairs, int E, int top, int N, int K, int gated, int dtype, cudaStream_t stream) {
+                                   int n_pairs, int E, int top, int N, int K, int mode, const float* in_scale, int dtype,
+                                   cudaStream_t stream) {
     if (n_pairs <= 0) return CPM_OK;
-    if (E < 1 || top < 1 || N < 1 || K < 1) return CPM_BAD_ARGUMENT;
+    if (E < 1 || top < 1 || N < 1 || K < 1 || mode < 0 || mode > 2) return CPM_BAD_ARGUMENT;
     if (dtype == CPM_BF16 && K % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)B0 & 15) == 0 && ((uintptr_t)B1 & 15) == 0 &&
         g_moe_tensor_cores) {
         const dim3 mgrid((n_pairs + kMmaM - 1) / kMmaM + E, (N + kMmaN - 1) / kMmaN);
         if (mgrid.y > 65535) return CPM_BAD_ARGUMENT;
-        if (gated)
-            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<true>, mgrid, dim3(256), 0, stream, (const bf16*)A, (const bf16*)B0,
-                       (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
-        else
-            cpm_launch(kLaunchProduct, moe_tile_mma_kernel<false>, mgrid, dim3(256), 0, stream, (const bf16*)A, (const bf16*)B0,
-                       (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K);
+#define CPM_MMA(M) cpm_launch(kLaunchProduct, moe_tile_mma_kernel<M>, mgrid, dim3(256), 0, stream, (const bf16*)A, (const bf16*)B0, \
+                              (const bf16*)B1, (bf16*)C, offsets, order, E, top, N, K, in_scale)
+        if (mode == 1) CPM_MMA(1); else if (mode == 2) CPM_MMA(2); else CPM_MMA(0);
+#undef CPM_MMA
         return launch_status();
     }
     const dim3 grid((n_pairs + kTileM - 1) / kTileM + E, (N + kTileN - 1) / kTileN);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
 #define CPM_MOE(TT, G) cpm_launch(kLaunchProduct, moe_tile_kernel<TT, G>, grid, dim3(256), 0, stream, (const TT*)A, (const TT*)B0, \
-                                  (const TT*)B1, (TT*)C, offsets, order, E, top, N, K)
-    if (dtype == CPM_BF16) { if (gated) CPM_MOE(bf16, true); else CPM_MOE(bf16, false); }
-    else { if (gated) CPM_MOE(float, true); else CPM_MOE(float, false); }
+                                  (const TT*)B1, (TT*)C, offsets, order, E, top, N, K, in_scale)
+    if (dtype == CPM_BF16) { if (mode == 1) CPM_MOE(bf16, 1); else if (mode == 2) CPM_MOE(bf16, 2); else CPM_MOE(bf16, 0); }
+    else { if (mode == 1) CPM_MOE(float, 1); else if (mode == 2) CPM_MOE(float, 2); else CPM_MOE(float, 0); }
 #undef CPM_MOE
     return launch_status();
 }

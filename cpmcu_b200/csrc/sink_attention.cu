@@ -2,8 +2,10 @@
 // prepares its queries and keys.
 //
 //   s(i, j) = q_i . k_j * scale;   s <- cap * tanh(s / cap)   (cap > 0)
-//   j is seen by i when 0 <= i - j < window   (window > 0; else every j <= i)
-//   p_j = exp(s_j) / (sink + sum_j' exp(s_j'))     sink = 1: one more key of score 0 that has no value; 0: plain softmax
+//   j is seen by i when j <= i and (i - j < window or j < keep_first)   (window > 0; else every j <= i)
+//   p_j = exp(s_j) / (exp(b_h) + sum_j' exp(s_j'))   sink: one more key without a value, whose score b_h is a number per
+//         head (``sinks``; null: 0) that is neither scaled nor capped; no sink: the plain softmax
+//   o_h <- o_h * sigmoid(gate[t][h])                 (``gate``: fp32 rows of ``gate_stride`` floats, one per head; null: none)
 //
 // Query and key heads have d channels, value heads dv.  Everything between the projections and the weighted sum of
 // values is fp32: biases, angles, the rotation, the unit root mean square of q and k, scores, cap, weights.
@@ -14,8 +16,8 @@ constexpr int kPrepMaxPerLane = 8;      // heads of up to 256 channels
 constexpr int kPrepWarps = 4;
 
 // proj: fp32 rows of ``stride`` floats, [heads*d | kv_heads*d | kv_heads*dv] (has_kv) or [heads*d].  One warp per
-// (token, head of q, k or v): adds the bias, turns the pairs (c, c + rot_dim/2) of the first rot_dim channels by
-// position * inv_freq[c], divides the head by its root mean square (unit_rms), and writes q to q_out [tokens, heads, d],
+// (token, head of q, k or v): adds the bias, turns the pairs (c, c + rot_dim/2) (``adjacent``: the pairs (2c, 2c + 1)) of
+// the first rot_dim channels by position * inv_freq[c], divides the head by its root mean square (unit_rms), and writes q to q_out [tokens, heads, d],
 // k into the key page and v (bias only) into the transposed value page of the token's position.
 template <typename T>
 __global__ void qk_prepare_store_kernel(const float* __restrict__ proj, int64_t stride, const float* __restrict__ q_bias,
@@ -23,8 +25,8 @@ __global__ void qk_prepare_store_kernel(const float* __restrict__ proj, int64_t 
                                         T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
-                                        const float* __restrict__ inv_freq, int rot_dim, int unit_rms, float eps,
-                                        int n_tokens, int n_heads, int n_kv, int d, int dv, int has_kv) {
+                                        const float* __restrict__ inv_freq, int rot_dim, int adjacent, int unit_rms,
+                                        float eps, int n_tokens, int n_heads, int n_kv, int d, int dv, int has_kv) {
     extern __shared__ float prep_smem[];       // [warps][d]
     pdl_launch_dependents();
     pdl_wait();
@@ -67,10 +69,12 @@ __global__ void qk_prepare_store_kernel(const float* __restrict__ proj, int64_t 
         if (c < d) {
             x = xs[c];
             if (inv_freq != nullptr && c < rot_dim) {
-                const int f = c < half ? c : c - half;
+                const int f = adjacent ? c >> 1 : (c < half ? c : c - half);
+                const bool first = adjacent ? !(c & 1) : c < half;
+                const int other = adjacent ? c ^ 1 : (first ? c + half : c - half);
                 float sn, cs;
                 sincosf((float)pos * inv_freq[f], &sn, &cs);
-                x = c < half ? x * cs - xs[c + half] * sn : x * cs + xs[c - half] * sn;
+                x = first ? x * cs - xs[other] * sn : x * cs + xs[other] * sn;
             }
         }
         val[i] = x;
@@ -89,8 +93,8 @@ __global__ void qk_prepare_store_kernel(const float* __restrict__ proj, int64_t 
 CPM_API int cpm_qk_prepare_store(const float* proj, int64_t stride, const float* q_bias, const float* k_bias,
                                  const float* v_bias, void* q_out, void* k_cache, void* v_cache, const int* positions,
                                  const int* token_seq, const int* slots, const int* page_table, int max_pages,
-                                 const float* inv_freq, int rot_dim, int unit_rms, float eps, int n_tokens, int n_heads,
-                                 int n_kv, int d, int dv, int has_kv, int dtype, cudaStream_t stream) {
+                                 const float* inv_freq, int rot_dim, int adjacent, int unit_rms, float eps, int n_tokens,
+                                 int n_heads, int n_kv, int d, int dv, int has_kv, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (d < 1 || d > 32 * kPrepMaxPerLane || dv < 1 || n_heads < 1 || n_kv < 1 || rot_dim < 0 || rot_dim > d || (rot_dim & 1))
         return CPM_BAD_ARGUMENT;
@@ -101,11 +105,11 @@ CPM_API int cpm_qk_prepare_store(const float* proj, int64_t stride, const float*
     if (dtype == CPM_BF16)
         cpm_launch(kLaunchRope, qk_prepare_store_kernel<bf16>, dim3((unsigned)blocks), dim3(kPrepWarps * 32), smem, stream, proj,
                    stride, q_bias, k_bias, v_bias, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, token_seq, slots,
-                   page_table, max_pages, inv_freq, rot_dim, unit_rms, eps, n_tokens, n_heads, n_kv, d, dv, has_kv);
+                   page_table, max_pages, inv_freq, rot_dim, adjacent, unit_rms, eps, n_tokens, n_heads, n_kv, d, dv, has_kv);
     else
         cpm_launch(kLaunchRope, qk_prepare_store_kernel<float>, dim3((unsigned)blocks), dim3(kPrepWarps * 32), smem, stream, proj,
                    stride, q_bias, k_bias, v_bias, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, token_seq, slots,
-                   page_table, max_pages, inv_freq, rot_dim, unit_rms, eps, n_tokens, n_heads, n_kv, d, dv, has_kv);
+                   page_table, max_pages, inv_freq, rot_dim, adjacent, unit_rms, eps, n_tokens, n_heads, n_kv, d, dv, has_kv);
     return launch_status();
 }
 
@@ -121,8 +125,9 @@ __global__ void sink_attention_generic_kernel(const T* __restrict__ q, const T* 
                                               const T* __restrict__ v_cache, T* __restrict__ out,
                                               const int* __restrict__ positions, const int* __restrict__ token_seq,
                                               const int* __restrict__ slots, const int* __restrict__ page_table,
-                                              int max_pages, int window, int n_heads, int n_kv, int d, int dv, float scale,
-                                              float cap, int sink) {
+                                              int max_pages, int window, int keep_first, int n_heads, int n_kv, int d, int dv,
+                                              float scale, float cap, int sink, const float* __restrict__ sinks,
+                                              const float* __restrict__ gate, int64_t gate_stride) {
     extern __shared__ float sink_q_smem[];   // [warps][d]
     pdl_launch_dependents();
     pdl_wait();
@@ -137,45 +142,51 @@ __global__ void sink_attention_generic_kernel(const T* __restrict__ q, const T* 
     const T* qrow = q + ((int64_t)t * n_heads + h) * d;
     for (int c = lane; c < d; c += 32) qs[c] = to_f32(qrow[c]);
     __syncwarp();
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    float m = sink ? (sinks ? sinks[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[kSinkMaxPerLane];
 #pragma unroll
     for (int i = 0; i < kSinkMaxPerLane; ++i) acc[i] = 0.f;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-    for (int j0 = lo; j0 <= p; j0 += 32) {
-        const int j = j0 + lane;
-        const bool valid = j <= p;
-        float s = -INFINITY;
-        if (valid) {
-            const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
-            const T* krow = k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d);
-            float dot = 0.f;
-            for (int c = 0; c < d; ++c) dot = fmaf(qs[c], to_f32(krow[c]), dot);
-            s = dot * scale;
-            if (cap > 0.f) s = cap * tanhf(s * inv_cap);
-        }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-        const float pr = valid ? expf(s - m_new) : 0.f;
-        l = l * corr + warp_sum(pr);
+    // two stretches of keys: the kept first tokens that lie before the window, then the window
+    const int kept_end = min(keep_first, lo);
+    for (int part = 0; part < 2; ++part) {
+        const int begin = part == 0 ? 0 : lo, end = part == 0 ? kept_end : p + 1;
+        for (int j0 = begin; j0 < end; j0 += 32) {
+            const int j = j0 + lane;
+            const bool valid = j < end;
+            float s = -INFINITY;
+            if (valid) {
+                const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
+                const T* krow = k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d);
+                float dot = 0.f;
+                for (int c = 0; c < d; ++c) dot = fmaf(qs[c], to_f32(krow[c]), dot);
+                s = dot * scale;
+                if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+            }
+            const float m_new = fmaxf(m, warp_max(s));
+            const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+            const float pr = valid ? expf(s - m_new) : 0.f;
+            l = l * corr + warp_sum(pr);
 #pragma unroll
-        for (int i = 0; i < kSinkMaxPerLane; ++i) acc[i] *= corr;
-        m = m_new;
-        const int n_here = min(32, p + 1 - j0);
-        for (int jj = 0; jj < n_here; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, pr, jj);
-            const int key = j0 + jj;
-            const int page = CPM_PAGE(pages, key / kPageTokens, max_pages);
-            const T* vcol = v_cache + value_offset(page, kvh, 0, key % kPageTokens, n_kv, dv);
+            for (int i = 0; i < kSinkMaxPerLane; ++i) acc[i] *= corr;
+            m = m_new;
+            const int n_here = min(32, end - j0);
+            for (int jj = 0; jj < n_here; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, pr, jj);
+                const int key = j0 + jj;
+                const int page = CPM_PAGE(pages, key / kPageTokens, max_pages);
+                const T* vcol = v_cache + value_offset(page, kvh, 0, key % kPageTokens, n_kv, dv);
 #pragma unroll
-            for (int i = 0; i < kSinkMaxPerLane; ++i) {
-                const int c = lane + 32 * i;
-                if (c < dv) acc[i] = fmaf(pj, to_f32(vcol[(int64_t)c * kPageTokens]), acc[i]);
+                for (int i = 0; i < kSinkMaxPerLane; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < dv) acc[i] = fmaf(pj, to_f32(vcol[(int64_t)c * kPageTokens]), acc[i]);
+                }
             }
         }
     }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-gate[(int64_t)t * gate_stride + h]));
     T* orow = out + ((int64_t)t * n_heads + h) * dv;
 #pragma unroll
     for (int i = 0; i < kSinkMaxPerLane; ++i) {
@@ -186,10 +197,12 @@ __global__ void sink_attention_generic_kernel(const T* __restrict__ q, const T* 
 
 CPM_API int cpm_sink_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                                        const int* token_seq, const int* slots, const int* page_table, int max_pages,
-                                       int window, int n_tokens, int n_heads, int n_kv, int d, int dv, float scale, float cap,
-                                       int sink, int dtype, cudaStream_t stream) {
+                                       int window, int keep_first, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                                       float scale, float cap, int sink, const float* sinks, const float* gate,
+                                       int64_t gate_stride, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (d <= 0 || dv <= 0 || dv > 32 * kSinkMaxPerLane || n_kv <= 0 || n_heads % n_kv != 0 || window < 0) return CPM_BAD_ARGUMENT;
+    if (d <= 0 || dv <= 0 || dv > 32 * kSinkMaxPerLane || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || keep_first < 0)
+        return CPM_BAD_ARGUMENT;
     const int warps = 4;
     dim3 grid(n_tokens, (n_heads + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
@@ -197,11 +210,11 @@ CPM_API int cpm_sink_attention_generic(const void* q, const void* k_cache, const
     if (dtype == CPM_BF16)
         cpm_launch(kLaunchAttention, sink_attention_generic_kernel<bf16>, grid, dim3(warps * 32), smem, stream, (const bf16*)q,
                    (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, window,
-                   n_heads, n_kv, d, dv, scale, cap, sink);
+                   keep_first, n_heads, n_kv, d, dv, scale, cap, sink, sinks, gate, gate_stride);
     else
         cpm_launch(kLaunchAttention, sink_attention_generic_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)q,
                    (const float*)k_cache, (const float*)v_cache, (float*)out, positions, token_seq, slots, page_table, max_pages,
-                   window, n_heads, n_kv, d, dv, scale, cap, sink);
+                   window, keep_first, n_heads, n_kv, d, dv, scale, cap, sink, sinks, gate, gate_stride);
     return launch_status();
 }
 
@@ -236,13 +249,14 @@ __device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint3
     lo = pack_bf16(a - __low2float(h), b - __high2float(h));
 }
 
-// 32 keys key0 .. key0 + 31 of one page; row r sees a key when lo[r] <= key <= hi[r].  The fragment loads:
+// 32 keys key0 .. key0 + 31 of one page; row r sees a key when lo[r] <= key <= hi[r], or key < keep_first and
+// key <= hi[r].  The fragment loads:
 // ``kload(t, w)`` gives the 8 channels 32 w + 8 j ... of key 8 (n / 2) + 2 t + (n & 1) of the 32, ``vload(nt)`` the
 // 8 tokens 8 j ... of value channel 8 nt + n  (j = lane % 4, n = lane / 4).
 template <int D, int DV, typename KLoad, typename VLoad>
 __device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (&q)[2][D / 32], KLoad kload, VLoad vload,
-                                                 int key0, const int (&lo)[2], const int (&hi)[2], float scale, float cap,
-                                                 int lane) {
+                                                 int key0, const int (&lo)[2], const int (&hi)[2], int keep_first,
+                                                 float scale, float cap, int lane) {
     constexpr float kLog2e = 1.4426950408889634f;
     const int j = lane & 3;
     float s[4][4];
@@ -265,7 +279,7 @@ __device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1, key = key0 + 8 * j + 2 * t + (e & 1);
             float x = cap > 0.f ? cap_log2 * tanh_by_exp(s[t][e] * scale * inv_cap) : s[t][e] * scale_log2;
-            x = (key >= lo[r] && key <= hi[r]) ? x : -INFINITY;
+            x = ((key >= lo[r] || key < keep_first) && key <= hi[r]) ? x : -INFINITY;
             s[t][e] = x;
             mx[r] = fmaxf(mx[r], x);
         }
@@ -322,20 +336,30 @@ __device__ __forceinline__ void sink_attend_keys(SinkTile<DV>& st, const uint4 (
     }
 }
 
-// Finishes a tile: the quad's shares of the sums join, the sink adds exp(0 - max), and rows [0, n_rows) go out as bf16.
-// out_row(r) gives the output row (dv channels) of tile row g + 8r.
+// The sink joins a finished row: with M = max(m, b) (b the sink's score in log2 units) the sum becomes
+// l 2^(m - M) + 2^(b - M) and the accumulator is scaled by 2^(m - M); returns that scale over the new sum.
+__device__ __forceinline__ float sink_join(float m, float l, int sink, float b) {
+    if (!sink) return l > 0.f ? 1.f / l : 0.f;
+    const float M = fmaxf(m, b);
+    const float f = m == -INFINITY ? 0.f : exp2f(m - M);
+    return f / (l * f + exp2f(b - M));
+}
+
+// Finishes a tile: the quad's shares of the sums join, the sink adds its term (score sink_log2[r] for tile row g + 8r), the
+// row is multiplied by row_gate[r], and rows go out as bf16.  out_row(r) gives the output row (dv channels) of tile row
+// g + 8r, or null.
 template <int DV, typename RowFn>
-__device__ __forceinline__ void sink_finish(SinkTile<DV>& st, int sink, int lane, RowFn out_row) {
+__device__ __forceinline__ void sink_finish(SinkTile<DV>& st, int sink, const float (&sink_log2)[2], const float (&row_gate)[2],
+                                            int lane, RowFn out_row) {
     const int j = lane & 3;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float l = st.l[r];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        if (sink) l += st.m[r] == -INFINITY ? 1.f : exp2f(-st.m[r]);
         bf16* orow = out_row(r);
         if (orow == nullptr) continue;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const float inv = sink_join(st.m[r], l, sink, sink_log2[r]) * row_gate[r];
 #pragma unroll
         for (int nt = 0; nt < DV / 8; ++nt)
             *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * j) = pack_bf16(st.o[nt][2 * r] * inv, st.o[nt][2 * r + 1] * inv);
@@ -364,8 +388,9 @@ __global__ void __launch_bounds__(kSinkTileWarps * 32)
 sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                             bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
                             const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
-                            const int* __restrict__ page_table, int max_pages, int window, int n_heads, int n_kv, float scale,
-                            float cap, int sink) {
+                            const int* __restrict__ page_table, int max_pages, int window, int keep_first, int n_heads, int n_kv,
+                            float scale, float cap, int sink, const float* __restrict__ sinks, const float* __restrict__ gate,
+                            int64_t gate_stride) {
     using S = SinkStage<D, DV>;
     extern __shared__ __align__(128) unsigned char sink_smem[];
     const uint32_t stages = (uint32_t)__cvta_generic_to_shared(sink_smem);
@@ -386,13 +411,19 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int last_page = (history + min(tile_row0 + kSinkTileRows, q_len) - 1) / kPageTokens;
     const int my_first = window > 0 ? max(0, history + row0 - window + 1) : 0;
     const int my_last = row0 < q_len ? history + min(row0 + 16, q_len) - 1 : -1;
+    // the pages of the kept first tokens that lie before the block's first page come first in the walk: step n of the
+    // walk is page n while n < kept_pages, then page first_page + n - kept_pages
+    const int kept_pages = min((keep_first + kPageTokens - 1) / kPageTokens, first_page);
+    const int n_steps = kept_pages + last_page - first_page + 1;
+    auto page_of = [&](int n) { return n < kept_pages ? n : first_page + n - kept_pages; };
 
-    auto issue = [&](int p) {
-        if (p <= last_page) {
+    auto issue = [&](int n) {
+        if (n < n_steps) {
+            const int p = page_of(n);
             const int page = CPM_PAGE(pages, p, max_pages);
             const bf16* kpage = k_cache + page_row_offset(page, kvh, 0, n_kv, D);
             const bf16* vpage = v_cache + value_offset(page, kvh, 0, 0, n_kv, DV);
-            const uint32_t stage = stages + ((p - first_page) & 1) * S::kBytes;
+            const uint32_t stage = stages + (n & 1) * S::kBytes;
 #pragma unroll 4
             for (int c = threadIdx.x; c < kPageTokens * S::kKeyChunks; c += kSinkTileWarps * 32) {
                 const int row = c / S::kKeyChunks, col = c % S::kKeyChunks;
@@ -407,8 +438,8 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         }
         cp_async_commit();
     };
-    issue(first_page);
-    issue(first_page + 1);
+    issue(0);
+    issue(1);
 
     uint4 qf[2][D / 32];
     int lo[2], hi[2];
@@ -424,14 +455,15 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
     SinkTile<DV> st;
     st.init();
-    for (int p = first_page; p <= last_page; ++p) {
+    for (int n = 0; n < n_steps; ++n) {
         cp_async_wait<1>();
         __syncthreads();
-        const uint32_t stage = stages + ((p - first_page) & 1) * S::kBytes;
+        const uint32_t stage = stages + (n & 1) * S::kBytes;
+        const int p = page_of(n);
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int key0 = p * kPageTokens + 32 * u;
-            if (key0 + 31 < my_first || key0 > my_last) continue;          // the same for the whole warp
+            if ((key0 + 31 < my_first && key0 >= keep_first) || key0 > my_last) continue;      // the same for the whole warp
             const int krow = 32 * u + 8 * (g >> 1) + (g & 1);
             sink_attend_keys<D, DV>(
                 st, qf,
@@ -444,14 +476,25 @@ sink_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                     const int row = 8 * nt + g;
                     return lds16(stage + S::kKeyBytes + (row * 8 + ((4 * u + j) ^ ((row & 1) << 2))) * 16);
                 },
-                key0, lo, hi, scale, cap, lane);
+                key0, lo, hi, keep_first, scale, cap, lane);
         }
         __syncthreads();
-        issue(p + 2);
+        issue(n + 2);
     }
     cp_async_wait<0>();
     if (row0 >= q_len) return;
-    sink_finish<DV>(st, sink, lane, [&](int r) -> bf16* {
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float b = sinks != nullptr ? sinks[h] * kLog2e : 0.f;
+    const float sink_log2[2] = {b, b};
+    float row_gate[2] = {1.f, 1.f};
+    if (gate != nullptr) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = min(row0 + g + 8 * r, q_len - 1);
+            row_gate[r] = 1.0f / (1.0f + __expf(-gate[(int64_t)(q_begin + row) * gate_stride + h]));
+        }
+    }
+    sink_finish<DV>(st, sink, sink_log2, row_gate, lane, [&](int r) -> bf16* {
         const int row = row0 + g + 8 * r;
         return row < q_len ? out + ((int64_t)(q_begin + row) * n_heads + h) * DV : nullptr;
     });
@@ -467,7 +510,9 @@ __global__ void __launch_bounds__(kSinkTokenWarps * 32)
 sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                             bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages, int window,
-                            int n_heads, int n_kv, float scale, float cap, int sink, float* __restrict__ shares) {
+                            int keep_first, int n_heads, int n_kv, float scale, float cap, int sink,
+                            const float* __restrict__ sinks, const float* __restrict__ gate, int64_t gate_stride,
+                            float* __restrict__ shares) {
     __shared__ float part_o[kSinkTokenWarps - 1][16][DV + 1];
     __shared__ float part_ml[kSinkTokenWarps - 1][16][2];
     pdl_launch_dependents();
@@ -495,19 +540,23 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     SinkTile<DV> st;
     st.init();
     const int first = (window > 0 ? max(0, p - window + 1) : 0) & ~31;
+    // the steps of 32 keys that hold kept first tokens before the window come first: step b of the walk begins at key 32 b
+    // while b < kept_steps, then at key first + 32 (b - kept_steps)
+    const int kept_steps = min((keep_first + 31) / 32, first / 32);
     // the token's steps of 32 keys go to gridDim.z blocks (shares != null when more than one), a block's to its warps
-    const int n_blocks = (p - first) / 32 + 1;
+    const int n_blocks = kept_steps + (p - first) / 32 + 1;
     const int per_block = (n_blocks + gridDim.z - 1) / gridDim.z;
     const int blk_begin = blockIdx.z * per_block, blk_end = min(n_blocks, blk_begin + per_block);
     const int share = (max(0, blk_end - blk_begin) + kSinkTokenWarps - 1) / kSinkTokenWarps;
     const int b_end = min(blk_end, blk_begin + (warp + 1) * share);
     for (int b = blk_begin + warp * share; b < b_end; ++b) {
-        const int key0 = first + 32 * b;
+        const int key0 = b < kept_steps ? 32 * b : first + 32 * (b - kept_steps);
         const int page = CPM_PAGE(pages, key0 / kPageTokens, max_pages), off = key0 % kPageTokens;
         const bf16* kp = k_cache + page_row_offset(page, kvh, off + 8 * (g >> 1) + (g & 1), n_kv, D) + 8 * j;
         const bf16* vp = v_cache + value_offset(page, kvh, g, off + 8 * j, n_kv, DV);
         sink_attend_keys<D, DV>(st, qf, [&](int t, int w) { return ldg16(kp + 2 * t * D + 32 * w); },
-                                [&](int nt) { return ldg16(vp + nt * 8 * kPageTokens); }, key0, lo, hi, scale, cap, lane);
+                                [&](int nt) { return ldg16(vp + nt * 8 * kPageTokens); }, key0, lo, hi, keep_first, scale, cap,
+                                lane);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -564,8 +613,8 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             if (j == 0) *reinterpret_cast<float2*>(dst + DV) = make_float2(m, l);
             continue;
         }
-        if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float inv = sink_join(m, l, sink, sinks != nullptr ? sinks[h0 + row] * 1.4426950408889634f : 0.f);
+        if (gate != nullptr) inv *= 1.0f / (1.0f + __expf(-gate[(int64_t)t * gate_stride + h0 + row]));
         bf16* orow = out + ((int64_t)t * n_heads + h0 + row) * DV + 2 * j;
 #pragma unroll
         for (int nt = 0; nt < DV / 8; ++nt)
@@ -573,10 +622,11 @@ sink_attention_token_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 }
 
-// out[t, h, :] = sum_s o_s 2^(m_s - M) / (sink 2^(-M) + sum_s l_s 2^(m_s - M)), M = max_s m_s, over the shares s of a
-// token's keys (rows of dv + 2 floats: o, m, l).  One warp per token and head.
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / (sink 2^(b_h - M) + sum_s l_s 2^(m_s - M)), M = max_s m_s, over the shares s of a
+// token's keys (rows of dv + 2 floats: o, m, l), times the head's gate.  One warp per token and head.
 __global__ void sink_combine_shares_kernel(const float* __restrict__ shares, bf16* __restrict__ out, int n_rows, int dv,
-                                           int n_splits, int sink) {
+                                           int n_splits, int sink, const float* __restrict__ sinks,
+                                           const float* __restrict__ gate, int64_t gate_stride, int n_heads) {
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -597,8 +647,10 @@ __global__ void sink_combine_shares_kernel(const float* __restrict__ shares, bf1
         for (int i = 0; i < 8; ++i)
             if (lane + 32 * i < dv) o[i] = fmaf(src[lane + 32 * i], f, o[i]);
     }
-    if (sink) l += m == -INFINITY ? 1.f : exp2f(-m);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const int h = row % n_heads;
+    float inv = sink_join(use, l, sink, sinks != nullptr ? sinks[h] * 1.4426950408889634f : 0.f);
+    if (m == -INFINITY) inv = 0.f;
+    if (gate != nullptr) inv *= 1.0f / (1.0f + __expf(-gate[(int64_t)(row / n_heads) * gate_stride + h]));
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         if (lane + 32 * i < dv) out[(int64_t)row * dv + lane + 32 * i] = __float2bfloat16(o[i] * inv);
@@ -608,8 +660,9 @@ template <int D, int DV>
 static int launch_sink_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                             const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* positions,
                             const int* token_seq, const int* slots, const int* page_table, int max_pages, int window,
-                            int n_tokens, int n_heads, int n_kv, float scale, float cap, int sink, float* shares,
-                            int n_splits, cudaStream_t stream) {
+                            int keep_first, int n_tokens, int n_heads, int n_kv, float scale, float cap, int sink,
+                            const float* sinks, const float* gate, int64_t gate_stride, float* shares, int n_splits,
+                            cudaStream_t stream) {
     if (n_tiles > 0) {
         auto kern = sink_attention_tiles_kernel<D, DV>;
         constexpr int smem = 2 * SinkStage<D, DV>::kBytes;
@@ -617,17 +670,19 @@ static int launch_sink_bf16(const void* q, const void* k_cache, const void* v_ca
         if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
         cpm_launch(kLaunchAttention, kern, dim3(n_heads, n_tiles), dim3(kSinkTileWarps * 32), smem,
                    stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q,
-                   kv_len, slots, page_table, max_pages, window, n_heads, n_kv, scale, cap, sink);
+                   kv_len, slots, page_table, max_pages, window, keep_first, n_heads, n_kv, scale, cap, sink, sinks, gate,
+                   gate_stride);
     } else {
         const int group = n_heads / n_kv;
         cpm_launch(kLaunchAttention, sink_attention_token_kernel<D, DV>,
                    dim3(n_tokens, n_kv * ((group + 15) / 16), n_splits), dim3(kSinkTokenWarps * 32), 0, stream, (const bf16*)q,
                    (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages,
-                   window, n_heads, n_kv, scale, cap, sink, n_splits > 1 ? shares : (float*)nullptr);
+                   window, keep_first, n_heads, n_kv, scale, cap, sink, sinks, gate, gate_stride,
+                   n_splits > 1 ? shares : (float*)nullptr);
         if (n_splits > 1) {
             const int n_rows = n_tokens * n_heads;
             cpm_launch(kLaunchAttention, sink_combine_shares_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream,
-                       (const float*)shares, (bf16*)out, n_rows, DV, n_splits, sink);
+                       (const float*)shares, (bf16*)out, n_rows, DV, n_splits, sink, sinks, gate, gate_stride, n_heads);
         }
     }
     return launch_status();
@@ -644,23 +699,51 @@ CPM_API int cpm_sink_attention_bf16_sizes(int d, int dv) {
 CPM_API int cpm_sink_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                                     const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len,
                                     const int* positions, const int* token_seq, const int* slots, const int* page_table,
-                                    int max_pages, int window, int n_tokens, int n_heads, int n_kv, int d, int dv, float scale,
-                                    float cap, int sink, float* shares, int n_splits, cudaStream_t stream) {
+                                    int max_pages, int window, int keep_first, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                                    float scale, float cap, int sink, const float* sinks, const float* gate,
+                                    int64_t gate_stride, float* shares, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (!cpm_sink_attention_bf16_sizes(d, dv) || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || n_tiles > 65535 ||
+    if (!cpm_sink_attention_bf16_sizes(d, dv) || n_kv <= 0 || n_heads % n_kv != 0 || window < 0 || keep_first < 0 || n_tiles > 65535 ||
         n_splits < 1 || n_splits > 65535 || (n_splits > 1 && !shares))
         return CPM_BAD_ARGUMENT;
     if (n_tiles > 0 ? (!tile_seq || !tile_row || !cu_q || !kv_len) : (!positions || !token_seq)) return CPM_BAD_ARGUMENT;
 #define CPM_SINK_CASE(DD, VV)                                                                                              \
     if (d == DD && dv == VV)                                                                                               \
         return launch_sink_bf16<DD, VV>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, positions,    \
-                                        token_seq, slots, page_table, max_pages, window, n_tokens, n_heads, n_kv, scale,   \
-                                        cap, sink, shares, n_splits, stream);
+                                        token_seq, slots, page_table, max_pages, window, keep_first, n_tokens, n_heads,    \
+                                        n_kv, scale, cap, sink, sinks, gate, gate_stride, shares, n_splits, stream);
 #define CPM_SINK_ROW(DD) CPM_SINK_CASE(DD, 32) CPM_SINK_CASE(DD, 64) CPM_SINK_CASE(DD, 96) CPM_SINK_CASE(DD, 128)
     CPM_SINK_ROW(32) CPM_SINK_ROW(64) CPM_SINK_ROW(96) CPM_SINK_ROW(128)
 #undef CPM_SINK_ROW
 #undef CPM_SINK_CASE
     return CPM_BAD_ARGUMENT;
+}
+
+// In place: x[t][h][:] *= sigmoid(gate[t][h]) (an output gate per head); gate: fp32 rows of ``gate_stride`` floats.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const float* __restrict__ gate, int64_t gate_stride, int64_t n, int n_heads,
+                                 int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t th = i / dv;
+    const float z = gate[(th / n_heads) * gate_stride + th % n_heads];
+    x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-z)));
+}
+
+CPM_API int cpm_head_gate(void* x, const float* gate, int64_t gate_stride, int n_tokens, int n_heads, int dv, int dtype,
+                          cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_heads < 1 || dv < 1 || !gate) return CPM_BAD_ARGUMENT;
+    const int64_t n = (int64_t)n_tokens * n_heads * dv;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == CPM_BF16)
+        cpm_launch(kLaunchOther, head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, gate, gate_stride, n, n_heads, dv);
+    else
+        cpm_launch(kLaunchOther, head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, gate, gate_stride, n, n_heads,
+                   dv);
+    return launch_status();
 }
 
 CPM_BOUNDS_TU(sink_attention)

@@ -57,7 +57,11 @@ _SIGNATURES = {
     "cpm_embed_sinusoid": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "cpm_act_mul": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_mingru_scan": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, _P],
-    "cpm_latent_norm_store": [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_latent_norm_store": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_float,
+                              c_int, _P],
+    "cpm_rotate_heads": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_head_gate": [_P, _P, c_int64, c_int, c_int, c_int, c_int, _P],
+    "cpm_channel_decay": [_P, _P, _P, c_int, c_int, c_int, _P],
     "cpm_head_project": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_rope_store_dv": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -73,12 +77,12 @@ _SIGNATURES = {
     "cpm_dual_rmsnorm_mean": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "cpm_gated_group_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_silu_columns": [_P, c_int64, c_int, c_int, _P],
-    "cpm_qk_prepare_store": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_float, c_int, c_int,
-                             c_int, c_int, c_int, c_int, c_int, _P],
-    "cpm_sink_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                   c_int, c_int, _P],
+    "cpm_qk_prepare_store": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_sink_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                   c_float, c_int, _P, _P, c_int64, c_int, _P],
     "cpm_sink_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_float, c_int, _P, c_int, _P],
+                                c_int, c_float, c_float, c_int, _P, _P, c_int64, _P, c_int, _P],
     "cpm_sink_attention_bf16_sizes": [c_int, c_int],
     "cpm_sink_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_int, c_float, c_int, _P, c_int, _P],
@@ -95,8 +99,8 @@ _SIGNATURES = {
     "cpm_set_recurrence_columns": [c_int],
     "cpm_moe_route": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "cpm_moe_group": [_P, c_int, c_int, _P, _P, _P],
-    "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
-    "cpm_moe_pair_product": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_moe_expert_product": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
+    "cpm_moe_pair_product": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "cpm_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "cpm_latent_attention_mma": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
 }

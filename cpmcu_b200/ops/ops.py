@@ -273,20 +273,53 @@ class Ops:
 
     # ---- attention over cached latents ----
     def latent_norm_store(self, ctx, proj: torch.Tensor, g_q: torch.Tensor, g_kv: torch.Tensor, lane, q_rank: int,
-                          rank: int, eps: float, write_cache: bool = True) -> torch.Tensor:
-        """proj fp32 [tokens, q_rank + rank]: RMS-norms both parts; returns the query latent [tokens, q_rank] and
-        stores the key-value latent into the lane's pages at each token's position."""
+                          rank: int, eps: float, write_cache: bool = True, rot_dim: int = 0,
+                          inv_freq: Optional[torch.Tensor] = None, adjacent: bool = False) -> torch.Tensor:
+        """proj fp32 rows that begin [q_rank | rank | rot_dim]: RMS-norms the first two parts; returns the query latent
+        [tokens, q_rank] and stores the key-value latent into the lane's pages at each token's position, followed (with
+        ``rot_dim``) by the third part turned by the position: pairs (i, i + rot_dim/2), or (2i, 2i + 1) with ``adjacent``,
+        angle position * inv_freq[i].  A cache row is [rank + rot_dim]."""
         self._f32(proj, "latent projections")
         n = proj.shape[0]
-        if proj.shape[1] != q_rank + rank:
-            raise ValueError("latent projections must be [tokens, q_rank + rank]")
+        if proj.shape[1] < q_rank + rank + rot_dim:
+            raise ValueError("latent projections must be [tokens, >= q_rank + rank + rot_dim]")
+        if rot_dim:
+            self._f32(inv_freq, "inv_freq")
+            if inv_freq.numel() != rot_dim // 2:
+                raise ValueError("inv_freq needs rot_dim/2 entries")
+        if write_cache and lane.k.shape[-1] != rank + rot_dim:
+            raise ValueError(f"latent_norm_store: the lane's rows hold {lane.k.shape[-1]} values, not {rank + rot_dim}")
         cq = self.empty(n, q_rank)
         cache = lane.k if write_cache else None
-        check(self.lib.cpm_latent_norm_store(_ptr(proj), _ptr(g_q), _ptr(g_kv), _ptr(cq), _ptr(cache), _ptr(ctx.positions),
-                                             _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
-                                             lane.page_table.shape[1], n, q_rank, rank, float(eps), self.code,
+        check(self.lib.cpm_latent_norm_store(_ptr(proj), proj.stride(0), _ptr(g_q), _ptr(g_kv), _ptr(cq), _ptr(cache),
+                                             _ptr(ctx.positions), _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
+                                             lane.page_table.shape[1], n, q_rank, rank, int(rot_dim),
+                                             _ptr(inv_freq) if rot_dim else None, 1 if adjacent else 0, float(eps), self.code,
                                              self._stream()), "latent_norm_store")
         return cq
+
+    def rotate_heads(self, ctx, x: torch.Tensor, n_heads: int, first: int, rot_dim: int, inv_freq: torch.Tensor,
+                     adjacent: bool = False) -> torch.Tensor:
+        """x fp32 [tokens, heads * dh] -> [tokens, heads * dh] in the compute dtype with the channels [first, first +
+        rot_dim) of every head turned by the token's position (pairs as in ``latent_norm_store``)."""
+        self._f32(x, "heads to rotate")
+        self._f32(inv_freq, "inv_freq")
+        n, dh = x.shape[0], x.shape[1] // n_heads
+        out = self.empty(n, n_heads * dh)
+        check(self.lib.cpm_rotate_heads(_ptr(x), _ptr(out), _ptr(ctx.positions), _ptr(inv_freq), n, n_heads, dh, int(first),
+                                        int(rot_dim), 1 if adjacent else 0, self.code, self._stream()), "rotate_heads")
+        return out
+
+    def head_gate(self, x: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor:
+        """In place: x [tokens, heads * dv] (compute dtype) times sigmoid(gate [tokens, heads]) head by head; the gate is
+        fp32 and may be a slice of wider rows."""
+        self._act(x, "heads to gate")
+        n = x.shape[0]
+        if gate.dtype != torch.float32 or gate.shape != (n, n_heads) or gate.stride(1) != 1:
+            raise ValueError("head_gate: the gate must be fp32 [tokens, heads]")
+        check(self.lib.cpm_head_gate(_ptr(x), _ptr(gate), gate.stride(0), n, n_heads, x.numel() // (n * n_heads), self.code,
+                                     self._stream()), "head_gate")
+        return x
 
     HEAD_PROJECT_LIBRARY_MIN_TOKENS = 64      # from this many tokens on, the per-head maps of the bf16 path are batched library products
 
@@ -815,12 +848,14 @@ class Ops:
         return out
 
     def conv_prepare(self, ctx, proj: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor,
-                     dt_bias: torch.Tensor, b_col: int, a_col: int, heads: int, qk_heads: int, d: int, dv: int, unit_eps: float):
+                     dt_bias: torch.Tensor, b_col: int, a_col: int, heads: int, qk_heads: int, d: int, dv: int, unit_eps: float,
+                     head_decay: bool = True):
         """proj fp32 [tokens, N] whose rows begin [q | k | v] and hold the raw gates at columns ``b_col`` and ``a_col``
         (one per head): short causal convolution (taps fp32 [channels, K], the last column the current token's) and SiLU
         on q, k, v; q and k heads scaled to unit length; beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)).
         conv_state fp32 [slots, K-1, channels] gives the inputs before the step and takes those after it.  Returns fp32
-        (q [tokens, qk_heads*d], k, v [tokens, heads*dv], beta [tokens, heads], decay [tokens, heads])."""
+        (q [tokens, qk_heads*d], k, v [tokens, heads*dv], beta [tokens, heads], decay [tokens, heads]); without
+        ``head_decay`` no decay is formed (None; ``a_log``, ``dt_bias`` and ``a_col`` are not read)."""
         self._f32(proj, "projections")
         self._f32(taps, "convolution taps")
         self._f32(conv_state, "convolution state")
@@ -832,7 +867,7 @@ class Ops:
         ko = self.empty(n, qk_heads * d, dtype=torch.float32)
         vo = self.empty(n, heads * dv, dtype=torch.float32)
         beta = self.empty(n, heads, dtype=torch.float32)
-        decay = self.empty(n, heads, dtype=torch.float32)
+        decay = self.empty(n, heads, dtype=torch.float32) if head_decay else None
         check(self.lib.cpm_conv_prepare(_ptr(proj), proj.stride(0), _ptr(taps), _ptr(conv_state), _ptr(ctx.positions),
                                         _ptr(ctx.token_seq), _ptr(ctx.cu_q), _ptr(ctx.slot_dev), _ptr(qo), _ptr(ko), _ptr(vo),
                                         _ptr(beta), _ptr(decay), _ptr(a_log), _ptr(dt_bias), int(b_col), int(a_col), n, ctx.n_seqs,
@@ -840,6 +875,17 @@ class Ops:
         if K > 1:
             LAUNCHES_EXTRA[0] += 1
         return qo, ko, vo, beta, decay
+
+    def channel_decay(self, z: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, heads: int, d: int) -> torch.Tensor:
+        """In place on fp32 [tokens, heads * d]: exp(-exp(a_log[h]) * softplus(z + dt_bias)), a decay per head and key
+        channel (a_log fp32 [heads], dt_bias fp32 [heads * d])."""
+        self._f32(z, "decay logits")
+        self._f32(a_log, "A_log")
+        self._f32(dt_bias, "dt_bias")
+        if z.shape[1] != heads * d or a_log.numel() != heads or dt_bias.numel() != heads * d:
+            raise ValueError("channel_decay: logits [tokens, heads * d], a_log [heads], dt_bias [heads * d]")
+        check(self.lib.cpm_channel_decay(_ptr(z), _ptr(a_log), _ptr(dt_bias), z.shape[0], heads, d, self._stream()), "channel_decay")
+        return z
 
     def sigmoid_power(self, z: torch.Tensor, bias: torch.Tensor, tau: float) -> torch.Tensor:
         """In place on fp32 [tokens, width]: sigmoid(z + bias)^(1/tau)."""
@@ -890,14 +936,14 @@ class Ops:
     # ---- attention with capped scores, a window and a sink ----
     def qk_prepare_store(self, ctx, proj: torch.Tensor, lane, n_heads: int, n_kv: int, d: int, dv: int,
                          biases, inv_freq: Optional[torch.Tensor], rot_dim: int, unit_rms: bool, eps: float,
-                         has_kv: bool = True) -> torch.Tensor:
+                         has_kv: bool = True, adjacent: bool = False, extra_cols: int = 0) -> torch.Tensor:
         """proj fp32 [tokens, heads*d + kv*d + kv*dv] (or [tokens, heads*d] without ``has_kv``): adds the biases
         (``biases`` = (q, k, v), fp32 or None each), rotates the first ``rot_dim`` channels of every q and k head
-        (pairs (i, i + rot_dim/2), angle position * inv_freq[i]), divides q and k heads by their root mean square
+        (pairs (i, i + rot_dim/2), or (2i, 2i + 1) with ``adjacent``; angle position * inv_freq[i]), divides q and k heads by their root mean square
         (``unit_rms``), stores k and v into the lane's pages and returns q [tokens, heads, d] in the compute dtype."""
         self._f32(proj, "projections")
         n = proj.shape[0]
-        if proj.shape[1] != n_heads * d + (n_kv * (d + dv) if has_kv else 0):
+        if proj.shape[1] != n_heads * d + (n_kv * (d + dv) if has_kv else 0) + int(extra_cols):      # extra_cols: what the caller keeps behind them
             raise ValueError("qk_prepare_store: the projections' row size does not match the head counts")
         if inv_freq is not None:
             self._f32(inv_freq, "inv_freq")
@@ -912,15 +958,19 @@ class Ops:
                                             _ptr(lane.k) if has_kv else None, _ptr(lane.v) if has_kv else None,
                                             _ptr(ctx.positions), _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
                                             lane.page_table.shape[1], _ptr(inv_freq) if rot_dim else None, int(rot_dim),
-                                            1 if unit_rms else 0, float(eps), n, n_heads, n_kv, d, dv, 1 if has_kv else 0,
+                                            1 if adjacent else 0, 1 if unit_rms else 0, float(eps), n, n_heads, n_kv, d, dv,
+                                            1 if has_kv else 0,
                                             self.code, self._stream()), "qk_prepare_store")
         return q
 
     def sink_attention(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int = 0, cap: float = 0.0,
-                       sink: bool = True) -> torch.Tensor:
+                       sink: bool = True, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """q [tokens, heads, d] over the lane's cached keys and values -> [tokens, heads*dv]: scores times ``scale``, capped
-        by cap * tanh(s / cap) when ``cap`` > 0, keys 0 <= i - j < ``window`` (0: all before and at i), softmax with one
-        added to the denominator when ``sink``.  Picks the kernel: bf16 with head sizes the tensor-core kernels are built
+        by cap * tanh(s / cap) when ``cap`` > 0, keys 0 <= i - j < ``window`` (0: all before and at i) and, with a window,
+        the keys j < ``keep_first`` too; softmax with exp(b_h) added to the denominator when ``sink`` (``sinks``: fp32
+        [heads], the b_h; None: 0); head h's output times sigmoid(gate[t][h]) (``gate``: fp32 [tokens, heads], may be a
+        slice of wider rows; None: none).  Picks the kernel: bf16 with head sizes the tensor-core kernels are built
         for goes to them (prompt tokens by the step's query tiles, anything else token by token); other sizes and the
         32-bit path go to the kernel of every size."""
         n, n_heads, d = q.shape
@@ -928,10 +978,22 @@ class Ops:
                 and os.environ.get("CPMCU_SINK_GENERIC", "0") != "1"):
             if (not ctx.is_decode and ctx.q_tiles is not None and ctx.max_q_len >= self.SINK_TCGEN05_MIN_ROWS
                     and self.use_tcgen05_attention and self.use_tcgen05_sink and d == dv and (n_heads // n_kv) % 2 == 0
-                    and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024))):
-                return self.sink_attention_tcgen05(ctx, q, lane, n_kv, scale, window, cap, sink)
-            return self.sink_attention_bf16(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
-        return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink)
+                    and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024)) and not (keep_first and window)
+                    and sinks is None):
+                out = self.sink_attention_tcgen05(ctx, q, lane, n_kv, scale, window, cap, sink)
+                return out if gate is None else self.head_gate(out, gate, n_heads)
+            return self.sink_attention_bf16(ctx, q, lane, n_kv, dv, scale, window, cap, sink, keep_first, sinks, gate)
+        return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink, keep_first, sinks, gate)
+
+    def _sink_extras(self, n: int, n_heads: int, window: int, keep_first: int, sinks, gate):
+        """Checked (keep_first, sinks pointer, gate pointer, gate stride) of the sink attention kernels."""
+        if sinks is not None:
+            self._f32(sinks, "sink scores")
+            if sinks.numel() != n_heads:
+                raise ValueError("sink scores: one number per head")
+        if gate is not None and (gate.dtype != torch.float32 or gate.shape != (n, n_heads) or gate.stride(1) != 1):
+            raise ValueError("the output gate must be fp32 [tokens, heads]")
+        return (int(keep_first) if window else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
 
     SINK_TCGEN05_MIN_ROWS = 32   # prompt portions from this many tokens on take the tcgen05 kernel's 128-row tiles
 
@@ -969,12 +1031,14 @@ class Ops:
     SINK_TILE_MIN_ROWS = 8       # shorter portions than this go token by token (a tile of 16 rows would be mostly empty)
 
     def sink_attention_bf16(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
-                            sink: bool) -> torch.Tensor:
+                            sink: bool, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                            gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The tensor-core kernels (bf16 operands; scores, cap, maxima, sums and accumulators fp32; a weight enters the
         product with the values as the sum of two bf16 numbers).  A warp owns 16 rows: query tokens of one head in a prompt
         (``ctx.q_tiles``), the query heads of one key-value head for a token taken alone."""
         self._act(q, "q")
         n, n_heads, d = q.shape
+        keep, p_sinks, p_gate, gate_stride = self._sink_extras(n, n_heads, window, keep_first, sinks, gate)
         out = self.empty(n, n_heads * dv)
         tiles = None if ctx.is_decode or ctx.max_q_len < self.SINK_TILE_MIN_ROWS else ctx.q_tiles
         tile_seq, tile_row, n_tiles = tiles if tiles is not None else (None, None, 0)
@@ -986,21 +1050,25 @@ class Ops:
         check(self.lib.cpm_sink_attention_bf16(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(tile_seq), _ptr(tile_row),
                                                int(n_tiles), _ptr(ctx.cu_q), _ptr(ctx.kv_len_dev), _ptr(ctx.positions),
                                                _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
-                                               lane.page_table.shape[1], int(window), n, n_heads, n_kv, d, dv, float(scale),
-                                               float(cap), 1 if sink else 0, _ptr(shares), n_splits, self._stream()),
+                                               lane.page_table.shape[1], int(window), keep, n, n_heads, n_kv, d, dv, float(scale),
+                                               float(cap), 1 if sink else 0, p_sinks, p_gate, gate_stride, _ptr(shares),
+                                               n_splits, self._stream()),
               f"sink attention on tensor cores ({n_heads} heads, {d} / {dv})")
         return out
 
     def sink_attention_generic(self, ctx, q: torch.Tensor, lane, n_kv: int, dv: int, scale: float, window: int, cap: float,
-                               sink: bool) -> torch.Tensor:
+                               sink: bool, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                               gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The kernel of every size and both precisions (one warp per token and head, fp32 arithmetic)."""
         self._act(q, "q")
         n, n_heads, d = q.shape
+        keep, p_sinks, p_gate, gate_stride = self._sink_extras(n, n_heads, window, keep_first, sinks, gate)
         out = self.empty(n, n_heads * dv)
         check(self.lib.cpm_sink_attention_generic(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(ctx.positions),
                                                   _ptr(ctx.token_seq), _ptr(ctx.slot_dev), _ptr(lane.page_table),
-                                                  lane.page_table.shape[1], int(window), n, n_heads, n_kv, d, dv, float(scale),
-                                                  float(cap), 1 if sink else 0, self.code, self._stream()),
+                                                  lane.page_table.shape[1], int(window), keep, n, n_heads, n_kv, d, dv,
+                                                  float(scale), float(cap), 1 if sink else 0, p_sinks, p_gate, gate_stride,
+                                                  self.code, self._stream()),
               f"sink attention ({n_heads} heads, {d} / {dv})")
         return out
 
@@ -1093,13 +1161,14 @@ class Ops:
 
     # ---- routed experts ----
     def moe_route(self, logits: torch.Tensor, correction: Optional[torch.Tensor], n_experts: int, top: int, n_groups: int, keep: int,
-                  gate_col: int = -1, bias: Optional[torch.Tensor] = None, top_first: bool = False):
+                  gate_col: int = -1, bias: Optional[torch.Tensor] = None, top_first: bool = False, sigmoid: bool = False):
         """logits fp32 [tokens, >= experts] -> (chosen int32 [tokens, top], weights fp32 [tokens, top], sigmoid of column
         ``gate_col`` fp32 [tokens] or None).  Default rule: softmax over all experts, choice by score + ``correction``
         within the kept groups, weights the plain scores.  ``top_first``: choice by logit + ``bias`` (fp32 [experts] or
-        None), weights the softmax over the chosen logits only."""
+        None), weights the softmax over the chosen logits only.  ``sigmoid``: scores are the sigmoids of the logits, the
+        largest are chosen and are the weights as they are."""
         self._f32(logits, "router logits")
-        if top_first:
+        if top_first or sigmoid:
             if bias is not None:
                 self._f32(bias, "router bias")
             if n_groups != 1:
@@ -1111,47 +1180,56 @@ class Ops:
         weights = self.empty(n, top, dtype=torch.float32)
         gate = self.empty(n, dtype=torch.float32) if gate_col >= 0 else None
         check(self.lib.cpm_moe_route(_ptr(logits), logits.shape[1], _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate),
-                                     int(gate_col), n, n_experts, top, n_groups, keep, _ptr(bias), 1 if top_first else 0,
+                                     int(gate_col), n, n_experts, top, n_groups, keep, _ptr(bias), 2 if sigmoid else (1 if top_first else 0),
                                      self._stream()),
               f"moe_route ({n_experts} experts, top {top})")
         return chosen, weights, gate
 
     MOE_PAIRWISE_MAX_PAIRS = int(os.environ.get("CPMCU_MOE_PAIRWISE_MAX", "96"))     # up to here a pair streams its expert alone
 
-    def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                    w_down: torch.Tensor) -> torch.Tensor:
+    def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, w_gate: Optional[torch.Tensor], w_up: torch.Tensor,
+                    w_down: torch.Tensor, input_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x [tokens, hidden]; chosen int32 [tokens, top]; stacks w_gate, w_up [experts, ff, hidden], w_down [experts,
-        hidden, ff] -> every pair's expert output, [tokens * top, hidden] in the compute dtype."""
+        hidden, ff] -> every pair's expert output, [tokens * top, hidden] in the compute dtype.  An expert is
+        down(silu(gate x) * up x), or without a gate stack (``w_gate`` None) down(relu(up (s x))^2) with s =
+        ``input_scale`` [tokens, top] (fp32; None: 1), applied to the up product's result, which is linear in x."""
         self._act(x, "expert input")
         for w, what in ((w_gate, "gate stack"), (w_up, "up stack"), (w_down, "down stack")):
-            self._act(w, what)
+            if w is not None:
+                self._act(w, what)
         n, hidden = x.shape
         top = chosen.shape[1]
-        E, ff, _ = w_gate.shape
+        E, ff, _ = w_up.shape
+        mode = 1 if w_gate is not None else 2
+        first, second = (w_gate, w_up) if mode == 1 else (w_up, None)
+        if input_scale is not None:
+            self._f32(input_scale, "expert input scale")
+            if mode == 1 or input_scale.shape != (n, top):
+                raise ValueError("moe_experts: an input scale [tokens, top] goes with experts that have no gate stack")
         pairs = n * top
         h = self.empty(pairs, ff)
         y = self.empty(pairs, hidden)
         if (self.code == BF16 and pairs <= self.MOE_PAIRWISE_MAX_PAIRS and hidden % 8 == 0 and ff % 8 == 0
                 and hidden <= 12288 and ff <= 12288):
             # few pairs (a decode step): every pair streams its expert's weights, no grouping
-            check(self.lib.cpm_moe_pair_product(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(h), _ptr(chosen), pairs, top, ff, hidden, 1,
-                                                self._stream()), "moe gate/up product by pair")
+            check(self.lib.cpm_moe_pair_product(_ptr(x), _ptr(first), _ptr(second), _ptr(h), _ptr(chosen), pairs, top, ff, hidden, mode,
+                                                _ptr(input_scale), self._stream()), "moe gate/up product by pair")
             check(self.lib.cpm_moe_pair_product(_ptr(h), _ptr(w_down), None, _ptr(y), _ptr(chosen), pairs, top, hidden, ff, 0,
-                                                self._stream()), "moe down product by pair")
+                                                None, self._stream()), "moe down product by pair")
             return y
         offsets = self.empty(E + 1, dtype=torch.int32)
         order = self.empty(pairs, dtype=torch.int32)
         check(self.lib.cpm_moe_group(_ptr(chosen), pairs, E, _ptr(offsets), _ptr(order), self._stream()), "moe_group")
-        check(self.lib.cpm_moe_expert_product(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(h), _ptr(offsets), _ptr(order), pairs, E, top,
-                                              ff, hidden, 1, self.code, self._stream()), "moe gate/up product")
+        check(self.lib.cpm_moe_expert_product(_ptr(x), _ptr(first), _ptr(second), _ptr(h), _ptr(offsets), _ptr(order), pairs, E, top,
+                                              ff, hidden, mode, _ptr(input_scale), self.code, self._stream()), "moe gate/up product")
         check(self.lib.cpm_moe_expert_product(_ptr(h), _ptr(w_down), None, _ptr(y), _ptr(offsets), _ptr(order), pairs, E, top,
-                                              hidden, ff, 0, self.code, self._stream()), "moe down product")
+                                              hidden, ff, 0, None, self.code, self._stream()), "moe down product")
         return y
 
-    def moe_combine(self, y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
-                    gate: Optional[torch.Tensor]) -> torch.Tensor:
-        """out[t] = sum_k weights[t][k] * y[t*top + k] (+ gate[t] * shared[t])."""
-        n, top = weights.shape
+    def moe_combine(self, y: torch.Tensor, weights: Optional[torch.Tensor], shared: Optional[torch.Tensor],
+                    gate: Optional[torch.Tensor], top: Optional[int] = None) -> torch.Tensor:
+        """out[t] = sum_k weights[t][k] * y[t*top + k] (+ gate[t] * shared[t]); without weights (``top`` given) the plain sum."""
+        n, top = weights.shape if weights is not None else (y.shape[0] // int(top), int(top))
         hidden = y.shape[1]
         out = self.empty(n, hidden)
         check(self.lib.cpm_moe_combine(_ptr(y), _ptr(weights), _ptr(shared), _ptr(gate), _ptr(out), n, top, hidden, self.code,

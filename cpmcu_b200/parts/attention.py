@@ -136,8 +136,11 @@ class SinkWindowAttention(Mixer):
         q, k <- position(q, k);   q, k <- x / sqrt(mean(x^2) + eps) per head          (``unit_rms``; no weight)
         s(i, j) = q_i . k_j * softmax_scale;   s <- softcap * tanh(s / softcap)        (``softcap`` > 0)
         j is seen by i when 0 <= i - j < window                                        (``window``; None: all j <= i)
-        p_j = exp(s_j) / (1 + sum_j' exp(s_j'))      (``sink``: a further key of score 0 without a value; else plain)
-        out = Wo [o_0 | o_1 | ...],  o_h = sum_j p_j v_kv(h)(j)
+            or j < keep_first and j <= i                                               (``keep_first``: tokens a window keeps)
+        p_j = exp(s_j) / (exp(b_h) + sum_j' exp(s_j'))      (``sink``: a further key without a value, of score b_h = 0, or with
+                                                             "learned" a number per head, tensor ``names["sink"]``; else plain)
+        o_h = sum_j p_j v_kv(h)(j);   o_h <- o_h * sigmoid(Wg h)_h                     (``gate``: ``names["gate"]`` [heads, hidden])
+        out = Wo [o_0 | o_1 | ...]
 
     With ``own_kv`` False the layer has no key and value projections: it reads the lane another layer of equal head
     counts and rotation wrote (keys as cached, after rotation and norm), with its own queries, window, cap and scale.
@@ -145,7 +148,7 @@ class SinkWindowAttention(Mixer):
     scores and weights are 32-bit; keys and values live in the cache in the compute dtype.
     """
 
-    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "bias": ".b"}
+    DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "bias": ".b", "sink": "sink", "gate": "g"}
 
     @property
     def recordable_prompt(self) -> bool:
@@ -153,7 +156,8 @@ class SinkWindowAttention(Mixer):
 
     def __init__(self, ops, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
                  softmax_scale: float, position: PartSpec, eps: float, window: Optional[int] = None, softcap: float = 0.0,
-                 sink: bool = True, unit_rms: bool = True, biases=("q", "k", "v"), own_kv: bool = True, names=None):
+                 sink=True, unit_rms: bool = True, biases=("q", "k", "v"), own_kv: bool = True, names=None,
+                 keep_first: int = 0, gate: bool = False):
         super().__init__(ops)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot be grouped over {n_kv_heads} key-value heads")
@@ -163,6 +167,10 @@ class SinkWindowAttention(Mixer):
         self.d, self.dv, self.scale, self.eps = int(head_dim), int(value_dim), float(softmax_scale), float(eps)
         self.window = int(window) if window else 0
         self.softcap, self.sink, self.unit_rms, self.own_kv = float(softcap or 0.0), bool(sink), bool(unit_rms), bool(own_kv)
+        self.learned_sink = sink == "learned"
+        self.keep_first = int(keep_first or 0) if self.window else 0
+        self.gate = bool(gate)
+        self.sinks: Optional[torch.Tensor] = None
         self.biases = tuple(b for b in ("q", "k", "v") if b in tuple(biases) and (b == "q" or self.own_kv))
         self.position = build_part(POSITIONS, position, ops)
         self.names = dict(self.DEFAULT_NAMES, **(dict(names) if names else {}))
@@ -175,6 +183,10 @@ class SinkWindowAttention(Mixer):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n, W = self.names, self.hidden_size
         specs = {n["o"]: WeightSpec((W, self.n_heads * self.dv))}
+        if self.learned_sink:
+            specs[n["sink"]] = WeightSpec((self.n_heads,), "vector")
+        if self.gate:
+            specs[n["gate"]] = WeightSpec((self.n_heads, W))
         for which, rows in self._projections():
             specs[n[which]] = WeightSpec((rows, W))
             if which in self.biases:
@@ -183,8 +195,11 @@ class SinkWindowAttention(Mixer):
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        self.w_in = self.ops.keep(torch.cat([tensors[n[which]] for which, _ in self._projections()], dim=0).contiguous())
+        rows = [tensors[n[which]] for which, _ in self._projections()] + ([tensors[n["gate"]]] if self.gate else [])
+        self.w_in = self.ops.keep(torch.cat(rows, dim=0).contiguous())       # one product: q (k, v) and the gates' logits
         self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
+        if self.learned_sink:
+            self.sinks = self.ops.keep(tensors[n["sink"]].float().contiguous())
         for which in self.biases:
             self.bias[which] = self.ops.keep(tensors[n[which] + n["bias"]].float().contiguous())
 
@@ -194,10 +209,10 @@ class SinkWindowAttention(Mixer):
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(kv_heads=self.n_kv, head_dim=self.d, window=self.window or None,
-                          value_dim=self.dv if self.dv != self.d else 0)
+                          value_dim=self.dv if self.dv != self.d else 0, keep_first=self.keep_first)
 
     def cache_bytes_read(self, kv_len: int) -> int:
-        keys = min(kv_len, self.window) if self.window else kv_len
+        keys = min(kv_len, self.window + self.keep_first) if self.window else kv_len
         return keys * self.n_kv * (self.d + self.dv) * self.ops.element_size
 
     def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
@@ -212,8 +227,12 @@ class SinkWindowAttention(Mixer):
             raise ValueError("sink_window_attention takes a rotation of pairs without a magnitude factor, or no position encoding")
         inv_freq, _, rot_dim = rot
         proj = ops.linear(y, self.w_in, out_f32=True)
-        q = ops.qk_prepare_store(ctx, proj, lane, self.n_heads, self.n_kv, self.d, self.dv,
+        H = self.n_heads
+        q = ops.qk_prepare_store(ctx, proj, lane, H, self.n_kv, self.d, self.dv,
                                  (self.bias["q"], self.bias["k"], self.bias["v"]), inv_freq if rot_dim else None, rot_dim,
-                                 self.unit_rms, self.eps, has_kv=self.own_kv)
-        out = ops.sink_attention(ctx, q, lane, self.n_kv, self.dv, self.scale, self.window, self.softcap, self.sink)
+                                 self.unit_rms, self.eps, has_kv=self.own_kv, adjacent=bool(getattr(self.position, "adjacent", False)),
+                                 extra_cols=H if self.gate else 0)
+        gate = proj[:, proj.shape[1] - H:] if self.gate else None
+        out = ops.sink_attention(ctx, q, lane, self.n_kv, self.dv, self.scale, self.window, self.softcap, self.sink,
+                                 keep_first=self.keep_first, sinks=self.sinks, gate=gate)
         return ops.linear(out, self.w_o)

@@ -156,7 +156,8 @@ class CacheNeeds:
     most recent tokens that do.  pooled_stride/pooled_kernel: an extra row per
     ``pooled_stride`` tokens (mean-pooled keys); 0 = none.  values: False when the
     lane keeps key rows only (a shared latent that keys and values are both made
-    from).  value_dim: the size of a value row where it differs from a key row's (0: the same).  state: tensors of fixed size per sequence, name -> (shape, dtype); they
+    from).  value_dim: the size of a value row where it differs from a key row's (0: the same).  keep_first: with a
+    window, the number of a sequence's first tokens that stay needed whatever the window.  state: tensors of fixed size per sequence, name -> (shape, dtype); they
     are zero when a sequence starts.
     """
 
@@ -168,9 +169,11 @@ class CacheNeeds:
     state: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]] = field(default_factory=dict)
     values: bool = True
     value_dim: int = 0
+    keep_first: int = 0
 
     def group_key(self) -> Tuple:
-        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values, self.value_dim)
+        return (self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, self.values, self.value_dim,
+                self.keep_first if self.window else 0)
 
     def seen_through(self, window: Optional[int]) -> "CacheNeeds":
         """The same needs when a further reader looks at the lane through ``window`` (None: at every key): the lane keeps
@@ -178,7 +181,7 @@ class CacheNeeds:
         if self.window is None or (window is not None and window <= self.window):
             return self
         return CacheNeeds(self.kv_heads, self.head_dim, window, self.pooled_stride, self.pooled_kernel, self.state, self.values,
-                          self.value_dim)
+                          self.value_dim, self.keep_first)
 
     def with_state(self, more: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]) -> "CacheNeeds":
         """The same needs with further per-sequence tensors (a block adds its own to its mixer's)."""
@@ -188,7 +191,7 @@ class CacheNeeds:
                 raise ValueError(f"per-sequence state '{name}' is declared twice for one lane")
             both[name] = what
         return CacheNeeds(self.kv_heads, self.head_dim, self.window, self.pooled_stride, self.pooled_kernel, both, self.values,
-                          self.value_dim)
+                          self.value_dim, self.keep_first)
 
 
 # ---------------------------------------------------------------------------

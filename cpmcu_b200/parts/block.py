@@ -35,6 +35,29 @@ class PreNormResidualBlock(Block):
         stream.add(f, self.residual_scale)
 
 
+@BLOCKS.register("parallel_residual")
+class ParallelResidualBlock(Block):
+    """x += s * (mixer(h) + feed_forward(h)) with h = norm(x): one norm, and both sublayers read its output.  The layer
+    has no second norm (``feed_forward_norm`` is None); without a feed-forward it is x += s * mixer(norm(x)).  The two
+    outputs are added to the 32-bit stream one after the other, the second inside the next layer's norm kernel."""
+
+    recordable_prompt = True
+
+    def __init__(self, ops, mixer, feed_forward, mixer_norm, feed_forward_norm, names, residual_scale: float = 1.0):
+        if feed_forward_norm is not None:
+            raise ValueError("parallel_residual: the layer has one norm; its feed-forward reads the mixer's input")
+        super().__init__(ops, mixer, feed_forward, mixer_norm, None, names)
+        self.residual_scale = float(residual_scale)
+
+    def forward(self, ctx, stream: ResidualStream, lane, writes_cache: bool) -> None:
+        h = stream.normed(self.mixer_norm)
+        a = self.mixer.forward(ctx, h, lane, writes_cache)
+        f = self.feed_forward.forward(ctx, h) if self.feed_forward is not None else None
+        stream.add(a, self.residual_scale)
+        if f is not None:
+            stream.add(f, self.residual_scale)
+
+
 @BLOCKS.register("sandwich_norm_shift")
 class SandwichNormShiftBlock(Block):
     """x += post1(mixer(shift(pre1(x)))); x += post2(feed_forward(pre2(x))): a norm before and after each sublayer,

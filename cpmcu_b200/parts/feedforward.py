@@ -80,6 +80,11 @@ class RoutedExperts(FeedForward):
     (``names["router_bias"]``, [experts]; ``router_bias`` False: none), the ``top`` largest are chosen, and the weights are
     the softmax over the chosen logits only; it has no correction tensor and no groups.
 
+    ``scoring`` "sigmoid": the scores are the sigmoids of the router's logits, the ``top`` largest are chosen and are the
+    weights as they are; no correction, bias or groups.  ``expert_form`` "up_relu2": an expert is down_e(relu(up_e x)^2)
+    with no gate matrix.  ``weight_on`` "input": out = sum over the chosen e of expert_e(s_e * y), the weight on what the
+    expert reads instead of on what it gives (it is applied to the up product's result, which is linear in its input).
+
     Expert e's matrices are ``<names["expert"]><e>.gate`` / ``.up`` / ``.down``; the shared expert's lie under
     ``names["shared"]`` with its gate vector ``names["shared_gate"]`` [1, hidden].  The router's product (with the
     shared gate's row appended) has 32-bit results; the experts' products run over the (token, expert) pairs grouped
@@ -89,17 +94,26 @@ class RoutedExperts(FeedForward):
     recordable_prompt = True
     DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e", "gate": ".gate", "up": ".up", "down": ".down",
                      "shared": "shared.", "shared_gate": "shared.sg", "router_bias": "router.b"}
-    SCORINGS = ("softmax_first", "top_first")
+    SCORINGS = ("softmax_first", "top_first", "sigmoid")
+    EXPERT_FORMS = ("gated_silu", "up_relu2")
 
     def __init__(self, ops, hidden_size: int, n_experts: int, top: int, expert_size: int, n_groups: int = 1, keep_groups: int = 1,
-                 shared_size: int = 0, names=None, scoring: str = "softmax_first", router_bias: bool = True):
+                 shared_size: int = 0, names=None, scoring: str = "softmax_first", router_bias: bool = True,
+                 expert_form: str = "gated_silu", weight_on: str = "output"):
         super().__init__(ops)
         if scoring not in self.SCORINGS:
             raise ValueError(f"routed_experts: scoring '{scoring}' is not built; known: {list(self.SCORINGS)}")
+        if expert_form not in self.EXPERT_FORMS or weight_on not in ("output", "input"):
+            raise ValueError(f"routed_experts: expert_form is one of {list(self.EXPERT_FORMS)}, weight_on 'output' or 'input'")
+        self.gated = expert_form == "gated_silu"
+        self.weight_on_input = weight_on == "input"
+        if self.weight_on_input and self.gated:
+            raise ValueError("routed_experts: the weight on an expert's input is built for experts without a gate matrix")
+        self.sigmoid = scoring == "sigmoid"
         self.top_first = scoring == "top_first"
         self.has_router_bias = self.top_first and bool(router_bias)
-        if self.top_first and int(n_groups) != 1:
-            raise ValueError("routed_experts: the rule that chooses first has no groups of experts")
+        if (self.top_first or self.sigmoid) and int(n_groups) != 1:
+            raise ValueError("routed_experts: this choice rule has no groups of experts")
         self.hidden_size, self.E, self.top, self.ff = int(hidden_size), int(n_experts), int(top), int(expert_size)
         self.n_groups, self.keep = int(n_groups), int(keep_groups)
         if self.E % self.n_groups or not 1 <= self.keep <= self.n_groups:
@@ -120,12 +134,13 @@ class RoutedExperts(FeedForward):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n, W, ff = self.names, self.hidden_size, self.ff
         out = {n["router"]: WeightSpec((self.E, W))}
-        if not self.top_first:
+        if not (self.top_first or self.sigmoid):
             out[n["correction"]] = WeightSpec((self.E,), "vector")
         if self.has_router_bias:
             out[n["router_bias"]] = WeightSpec((self.E,), "vector")
         for e in range(self.E):
-            out[self._expert(e, "gate")] = WeightSpec((ff, W))
+            if self.gated:
+                out[self._expert(e, "gate")] = WeightSpec((ff, W))
             out[self._expert(e, "up")] = WeightSpec((ff, W))
             out[self._expert(e, "down")] = WeightSpec((W, ff))
         if self.shared is not None:
@@ -138,9 +153,10 @@ class RoutedExperts(FeedForward):
         n = self.names
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared is not None else [])
         self.w_router = self.ops.keep(torch.cat(rows, dim=0).contiguous())
-        self.correction = self.ops.keep(tensors[n["correction"]].float().contiguous()) if not self.top_first else None
+        self.correction = self.ops.keep(tensors[n["correction"]].float().contiguous()) if n["correction"] in tensors else None
         self.router_bias = self.ops.keep(tensors[n["router_bias"]].float().contiguous()) if self.has_router_bias else None
-        self.w_gate = self.ops.keep(torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)]).contiguous())
+        self.w_gate = self.ops.keep(torch.stack([tensors[self._expert(e, "gate")] for e in range(self.E)]).contiguous()) \
+            if self.gated else None
         self.w_up = self.ops.keep(torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous())
         self.w_down = self.ops.keep(torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous())
         if self.shared is not None:
@@ -148,7 +164,7 @@ class RoutedExperts(FeedForward):
 
     def weight_bytes(self) -> int:
         """What a decode step of one token reads: the router, ``top`` experts, the shared expert."""
-        per_expert = 3 * self.ff * self.hidden_size * self.w_gate.element_size()
+        per_expert = (3 if self.gated else 2) * self.ff * self.hidden_size * self.w_up.element_size()
         total = self.w_router.numel() * self.w_router.element_size() + self.top * per_expert
         return total + (self.shared.weight_bytes() if self.shared is not None else 0)
 
@@ -157,10 +173,11 @@ class RoutedExperts(FeedForward):
         logits = ops.linear(y, self.w_router, out_f32=True)
         chosen, weights, gate = ops.moe_route(logits, self.correction, self.E, self.top, self.n_groups, self.keep,
                                               gate_col=self.E if self.shared is not None else -1, bias=self.router_bias,
-                                              top_first=self.top_first)
+                                              top_first=self.top_first, sigmoid=self.sigmoid)
         taps = ctx.extras.get("taps")
         if taps is not None and not ctx.captured and taps.get("experts") is not None:
             taps["experts"].append(chosen.clone())          # a caller that wants to see the choice (tests do)
-        pairs = ops.moe_experts(y, chosen, self.w_gate, self.w_up, self.w_down)
+        pairs = ops.moe_experts(y, chosen, self.w_gate, self.w_up, self.w_down,
+                                input_scale=weights if self.weight_on_input else None)
         shared = self.shared.forward(ctx, y) if self.shared is not None else None
-        return ops.moe_combine(pairs, weights, shared, gate)
+        return ops.moe_combine(pairs, None if self.weight_on_input else weights, shared, gate, top=self.top)

@@ -92,15 +92,23 @@ class GatedDeltaRule(_MatrixStateMixer):
     q and k have ``n_qk_heads`` heads; value head h uses q/k head h / (heads / qk_heads).  Besides S the last K-1
     inputs of the convolutions are per-sequence state.  ``names``: "q", "k", "v" (their taps under ``<name>.conv``),
     "b", "a", "A_log", "dt_bias", "g", "o", "norm".
+
+    With ``decay_rank`` the decay is one number per head and key channel, acting on the rows of S, through two projections:
+    g = exp(-exp(A_log_h) * softplus(Wa2 (Wa1 h) + dt_bias)), laid out heads x d (Wa1 [rank, hidden] ``names["a1"]``, Wa2
+    [heads * d, rank] ``names["a2"]``, dt_bias [heads * d]).  With ``gate_rank`` the output gate is gate(Wg2 (Wg1 h))
+    (``names["g1"]``, ``names["g2"]``) instead of gate(Wg h); ``gate``: "silu" or "sigmoid".
     """
 
     DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "conv": ".conv", "b": "b", "a": "a", "A_log": "A_log", "dt_bias": "dt_bias",
-                     "g": "g", "o": "o", "norm": "norm"}
+                     "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "g1": "g1", "g2": "g2"}
     UNIT_EPS = 1e-6
 
     def __init__(self, ops, hidden_size: int, n_heads: int, n_qk_heads: int, head_dim: int, value_dim: int, conv_taps: int,
-                 eps: float, names=None):
+                 eps: float, names=None, decay_rank: int = 0, gate_rank: int = 0, gate: str = "silu"):
         super().__init__(ops)
+        self.decay_rank, self.gate_rank, self.gate = int(decay_rank or 0), int(gate_rank or 0), str(gate)
+        if self.gate not in ("silu", "sigmoid"):
+            raise ValueError(f"gated_delta_rule: the gate is 'silu' or 'sigmoid', not '{gate}'")
         self.hidden_size, self.heads, self.qk_heads = int(hidden_size), int(n_heads), int(n_qk_heads)
         self.d, self.dv, self.taps, self.eps = int(head_dim), int(value_dim), int(conv_taps), float(eps)
         if self.heads % self.qk_heads:
@@ -112,16 +120,47 @@ class GatedDeltaRule(_MatrixStateMixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n, W, H, G, d, dv, K = self.names, self.hidden_size, self.heads, self.qk_heads, self.d, self.dv, self.taps
-        return {n["q"]: WeightSpec((G * d, W)), n["q"] + n["conv"]: WeightSpec((G * d, K), "vector"),
-                n["k"]: WeightSpec((G * d, W)), n["k"] + n["conv"]: WeightSpec((G * d, K), "vector"),
-                n["v"]: WeightSpec((H * dv, W)), n["v"] + n["conv"]: WeightSpec((H * dv, K), "vector"),
-                n["b"]: WeightSpec((H, W)), n["a"]: WeightSpec((H, W)), n["A_log"]: WeightSpec((H,), "vector"),
-                n["dt_bias"]: WeightSpec((H,), "vector"), n["g"]: WeightSpec((H * dv, W)), n["o"]: WeightSpec((W, H * dv)),
-                n["norm"]: WeightSpec((dv,), "vector")}
+        out = {n["q"]: WeightSpec((G * d, W)), n["q"] + n["conv"]: WeightSpec((G * d, K), "vector"),
+               n["k"]: WeightSpec((G * d, W)), n["k"] + n["conv"]: WeightSpec((G * d, K), "vector"),
+               n["v"]: WeightSpec((H * dv, W)), n["v"] + n["conv"]: WeightSpec((H * dv, K), "vector"),
+               n["b"]: WeightSpec((H, W)), n["A_log"]: WeightSpec((H,), "vector"), n["o"]: WeightSpec((W, H * dv)),
+               n["norm"]: WeightSpec((dv,), "vector")}
+        if self.decay_rank:
+            out.update({n["a1"]: WeightSpec((self.decay_rank, W)), n["a2"]: WeightSpec((H * d, self.decay_rank)),
+                        n["dt_bias"]: WeightSpec((H * d,), "vector")})
+        else:
+            out.update({n["a"]: WeightSpec((H, W)), n["dt_bias"]: WeightSpec((H,), "vector")})
+        if self.gate_rank:
+            out.update({n["g1"]: WeightSpec((self.gate_rank, W)), n["g2"]: WeightSpec((H * dv, self.gate_rank))})
+        else:
+            out[n["g"]] = WeightSpec((H * dv, W))
+        return out
+
+    def _fused(self):
+        """What the one product of the layer's input gives, in the order of its columns: (name, columns)."""
+        H, G, d, dv = self.heads, self.qk_heads, self.d, self.dv
+        cols = [("q", G * d), ("k", G * d), ("v", H * dv)]
+        if not self.gate_rank:
+            cols.append(("g", H * dv))
+        cols.append(("b", H))
+        if not self.decay_rank:
+            cols.append(("a", H))
+        if self.gate_rank:
+            cols.append(("g1", self.gate_rank))
+        if self.decay_rank:
+            cols.append(("a1", self.decay_rank))
+        return cols
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        self.w_in = self.ops.keep(torch.cat([tensors[n[x]] for x in ("q", "k", "v", "g", "b", "a")], dim=0).contiguous())
+        self.w_in = self.ops.keep(torch.cat([tensors[n[x]] for x, _ in self._fused()], dim=0).contiguous())
+        self.col = {}
+        at = 0
+        for x, width in self._fused():
+            self.col[x] = at
+            at += width
+        self.w_a2 = self.ops.keep(tensors[n["a2"]].contiguous()) if self.decay_rank else None
+        self.w_g2 = self.ops.keep(tensors[n["g2"]].contiguous()) if self.gate_rank else None
         self.w_o = self.ops.keep(tensors[n["o"]].contiguous())
         self.w_taps = self._keep32(torch.cat([tensors[n[x] + n["conv"]].float() for x in ("q", "k", "v")], dim=0))
         self.a_log = self._keep32(tensors[n["A_log"]])
@@ -129,7 +168,8 @@ class GatedDeltaRule(_MatrixStateMixer):
         self.w_norm = self._keep32(tensors[n["norm"]])
 
     def weight_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_taps, self.a_log, self.dt_bias, self.w_norm))
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_taps, self.a_log, self.dt_bias, self.w_norm,
+                                                          self.w_a2, self.w_g2) if t is not None)
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(state={"matrix_state": ((self.heads, self.d, self.dv), torch.float32),
@@ -140,13 +180,31 @@ class GatedDeltaRule(_MatrixStateMixer):
 
     def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
         ops, H, G, d, dv = self.ops, self.heads, self.qk_heads, self.d, self.dv
-        C = self.channels
-        proj = ops.linear(y, self.w_in, out_f32=True)                       # [q | k | v | g | b | a]
-        b_col = C + H * dv
+        col = self.col
+        proj = ops.linear(y, self.w_in, out_f32=True)                       # [q | k | v | (g) | b | (a) | (g1) | (a1)]
         q, k, v, beta, decay = ops.conv_prepare(ctx, proj, self.w_taps, lane.state["conv_inputs"], self.a_log, self.dt_bias,
-                                                b_col, b_col + H, H, G, d, dv, self.UNIT_EPS)
-        o = ops.linear_recurrence(ctx, q, k, v, decay, beta, lane.state["matrix_state"], H, G, d, dv, d ** -0.5)
-        return ops.linear(ops.gated_head_norm(o, proj[:, C:C + H * dv], self.w_norm, self.eps), self.w_o)
+                                                col["b"], col.get("a", 0), H, G, d, dv, self.UNIT_EPS,
+                                                head_decay=not self.decay_rank)
+        if self.decay_rank:
+            # the second projection takes the first's result in the compute dtype; its own result, the softplus, the
+            # exponentials and the decay are 32-bit
+            low = self._narrow(proj, col["a1"], self.decay_rank)
+            decay = ops.channel_decay(ops.linear(low, self.w_a2, out_f32=True), self.a_log, self.dt_bias, H, d)
+        o = ops.linear_recurrence(ctx, q, k, v, decay, beta, lane.state["matrix_state"], H, G, d, dv, d ** -0.5,
+                                  vector_decay=bool(self.decay_rank))
+        if self.gate_rank:
+            gate = ops.linear(self._narrow(proj, col["g1"], self.gate_rank), self.w_g2, out_f32=True)
+        else:
+            gate = proj[:, col["g"]:col["g"] + H * dv]
+        if self.gate == "silu":
+            return ops.linear(ops.gated_head_norm(o, gate, self.w_norm, self.eps), self.w_o)
+        return ops.linear(ops.gated_group_norm(o, gate, self.w_norm, self.eps, 1, self.gate), self.w_o)
+
+    def _narrow(self, proj: torch.Tensor, first: int, width: int) -> torch.Tensor:
+        """Columns of the fused product as a contiguous operand of the next product (compute dtype)."""
+        out = self.ops.empty(proj.shape[0], width)
+        out.copy_(proj[:, first:first + width])
+        return out
 
 
 @MIXERS.register("lightning_attention")

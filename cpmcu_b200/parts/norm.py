@@ -1,7 +1,7 @@
 """Norms of the residual stream.
 
 RMS norm (src/model/norm.cuh:7-51): y = x * rsqrt(mean(x^2) + eps) * weight, the weight
-used as it is stored (not 1 + weight).  Layer norm: y = (x - mean) / sqrt(var + eps) * weight + bias with var
+used as it is stored (not 1 + weight) unless the part is given an ``offset``.  Layer norm: y = (x - mean) / sqrt(var + eps) * weight + bias with var
 the mean of the squared deviations; the reference has none."""
 from __future__ import annotations
 
@@ -16,19 +16,24 @@ from .base import NORMS, Norm, WeightSpec
 class RMSNorm(Norm):
     recordable_prompt = True
 
-    def __init__(self, ops, hidden_size: int, eps: float, weight_name: str = "weight"):
-        """``weight_name``: the tensor's name below the part's prefix."""
+    def __init__(self, ops, hidden_size: int, eps: float, weight_name: str = "weight", offset: float = 0.0):
+        """``weight_name``: the tensor's name below the part's prefix.  ``offset``: a constant added to the stored weight
+        (1 for a weight that is stored around zero: y = x / rms * (1 + w)); the sum is formed once, in 32-bit."""
         super().__init__(ops)
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)
         self.weight_name = str(weight_name)
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {self.weight_name: WeightSpec((self.hidden_size,), "vector")}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = self.ops.keep(tensors[self.weight_name].contiguous())
+        w = tensors[self.weight_name]
+        if self.offset:
+            w = w.float() + self.offset
+        self.weight = self.ops.keep(w.contiguous())
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

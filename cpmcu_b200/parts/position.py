@@ -40,6 +40,7 @@ class NoPosition(PositionEncoding):
 @POSITIONS.register("rope")
 class Rotary(PositionEncoding):
     recordable_prompt = True
+    adjacent = False            # which channels form a pair: (i, i + rot_dim/2), or with ``adjacent`` (2i, 2i + 1)
 
     def __init__(self, ops, head_dim: int, theta: float, rot_dim: Optional[int] = None):
         super().__init__(ops)
@@ -74,6 +75,31 @@ class LinearlyScaledRotary(Rotary):
         i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
         table = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / max(self.rot_dim, 1)) / self.factor
         self.inv_freq = table.to(torch.float32).to(self.ops.device if self.ops is not None else "cpu")
+
+
+@POSITIONS.register("wavelength_scaled_rope")
+class WavelengthScaledRotary(Rotary):
+    """A rotation of the first ``rot_dim`` channels of a head in adjacent pairs (2i, 2i + 1) (``adjacent`` False: pairs
+    (i, i + rot_dim/2)), f_i = theta^(-2i/rot_dim), with the frequencies stretched by wavelength when ``factor`` is given:
+    with l = 2 pi / f, a wave shorter than original / high keeps f, one longer than original / low gets f / factor, and
+    between the two f becomes (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  The table is formed
+    in 64-bit on the host and rounded once to 32-bit; angles are 32-bit on the device."""
+
+    def __init__(self, ops, head_dim: int, theta: float, rot_dim: Optional[int] = None, factor: Optional[float] = None,
+                 low: float = 1.0, high: float = 4.0, original: int = 8192, adjacent: bool = True):
+        super().__init__(ops, head_dim, theta, rot_dim)
+        self.adjacent = bool(adjacent)
+        i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / max(self.rot_dim, 1))
+        if factor is not None:
+            factor, low, high, original = float(factor), float(low), float(high), float(original)
+            if not (factor > 0 and high > low and original > 0):
+                raise ValueError("wavelength_scaled_rope: needs factor > 0, high > low and original > 0")
+            wave = 2.0 * math.pi / f
+            blend = (original / wave - low) / (high - low)
+            mid = (1.0 - blend) * f / factor + blend * f
+            f = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, mid))
+        self.inv_freq = f.to(torch.float32).to(self.ops.device if self.ops is not None else "cpu")
 
 
 @POSITIONS.register("longrope")

@@ -117,6 +117,11 @@ def _register_builtin() -> None:
     from .models import kipizen
 
     register_architecture(Architecture(name=KipizenConfig.architecture, config_class=KipizenConfig, model_spec=kipizen.model_spec))
+    from .config.lukelorn import LukelornConfig
+    from .models import lukelorn
+
+    register_architecture(Architecture(name=LukelornConfig.architecture, config_class=LukelornConfig, model_spec=lukelorn.model_spec,
+                                       fit_config=lukelorn.fit_config_to_checkpoint))
 
 
 _register_builtin()
