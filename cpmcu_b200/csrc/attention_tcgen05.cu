@@ -91,13 +91,18 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // What the sink window attention adds to the kernel below (kSink): keys no further back than ``window`` tokens
-// (0: all), scores capped as cap * tanh(s / cap) (cap_log2 = cap * log2(e), 0: no cap; pre = scale / cap), and a sink of
-// score 0 without a value in the softmax's denominator.
+// (0: all) beside a sequence's first ``keep_first`` tokens, scores capped as cap * tanh(s / cap) (cap_log2 = cap * log2(e),
+// 0: no cap; pre = scale / cap), a sink without a value in the softmax's denominator whose score is 0 or a number per head
+// (``sinks``), and an output gate per head: o_h <- o_h sigmoid(gate[token][h]) (``gate`` null: none).
 struct SinkExtras {
     int window;
     float cap_log2;
     float pre;
     int sink;
+    int keep_first;
+    const float* sinks;
+    const float* gate;
+    int64_t gate_stride;
 };
 
 template <int kD, bool kSink>
@@ -132,12 +137,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // With n_splits > 1 (few query tiles, many keys: a short chunk after a long history) the key steps of a tile
     // are shared out over gridDim.z blocks, which leave unnormalised partial results for a second kernel.
     // With a window the tile's first key step is the one that holds the first key of its first token.
+    // The steps that hold kept first tokens before that one come first in the walk: place n of the walk is key step n
+    // while n < kept_steps, then key step step0 + n - kept_steps.
     const int window = kSink ? extras.window : 0;
+    const int keep_first = (kSink && window > 0) ? extras.keep_first : 0;
     const int step0 = window > 0 ? max(0, history + tile_row0 - window + 1) / kBlockKeys : 0;
-    const int all_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys - step0;
+    const int kept_steps = min((keep_first + kBlockKeys - 1) / kBlockKeys, step0);
+    const int all_blocks = kept_steps + (n_keys + kBlockKeys - 1) / kBlockKeys - step0;
     const int per_split = (all_blocks + n_splits - 1) / n_splits;
-    const int j_first = step0 + (int)blockIdx.z * per_split;
-    const int n_blocks = max(0, min(step0 + all_blocks, j_first + per_split) - j_first);      // key steps of this block
+    const int j_first = (int)blockIdx.z * per_split;                                          // a place of the walk
+    const int n_blocks = max(0, min(all_blocks, j_first + per_split) - j_first);              // key steps of this block
+    auto step_of = [&](int n) { return n < kept_steps ? n : step0 + n - kept_steps; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzled tiles want 1 KiB alignment
@@ -190,8 +200,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int j = 0; j < n_blocks && !aborted(); ++j, ++issued) {
                 const int s = j & 1, ph = (j >> 1) & 1;
                 // the second page of the last step may lie beyond the keys: its scores are masked, any page will do
-                const int pa = min(max(CPM_PAGE(pages, 2 * (j_first + j), max_pages), 0), n_pages - 1);
-                const int pb = min(max(CPM_PAGE(pages, min(2 * (j_first + j) + 1, last_page), max_pages), 0), n_pages - 1);
+                const int step = step_of(j_first + j);
+                const int pa = min(max(CPM_PAGE(pages, 2 * step, max_pages), 0), n_pages - 1);
+                const int pb = min(max(CPM_PAGE(pages, min(2 * step + 1, last_page), max_pages), 0), n_pages - 1);
                 if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ph ^ 1)) { fail(ERR_K_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&k_full[s]), kTileBytes);
                 for (int half = 0; half < Z::kHalves; ++half) {
@@ -293,7 +304,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_load_32cols(s_addr + c * 32, v[c]);
             tmem_load_wait();
-            const int key0 = (j_first + j) * kBlockKeys;
+            const int key0 = step_of(j_first + j) * kBlockKeys;
             if constexpr (kSink) {
                 if (extras.cap_log2 > 0.f) {
                     // cap * tanh(s / cap) in log2 units, tanh(x) = 1 - 2 / (e^(2x) + 1): exact limits at both ends
@@ -314,7 +325,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
                         for (int e = 0; e < 32; ++e)
-                            if (key0 + c * 32 + e > limit || key0 + c * 32 + e < first) v[c][e] = 0xff800000u;      // -inf
+                            if (key0 + c * 32 + e > limit || (key0 + c * 32 + e < first && key0 + c * 32 + e >= keep_first))
+                                v[c][e] = 0xff800000u;      // -inf
                 }
             } else if (key0 + kBlockKeys - 1 > history + tile_row0) {   // the diagonal, or the end of the keys
 #pragma unroll
@@ -368,8 +380,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[i]));
         }
-        // the sink: one more term of score 0 (with shares of the keys, the kernel that joins them adds it)
-        if (kSink && extras.sink && n_splits == 1) l += m_ref == -INFINITY ? 1.f : ex2(-m_ref);
+        // the sink: one more term of score 0, or of the head's own score (with shares of the keys, the kernel that joins
+        // them adds it)
+        if (kSink && extras.sink && n_splits == 1) {
+            const float b = extras.sinks != nullptr ? extras.sinks[h0 + i] * 1.4426950408889634f : 0.f;
+            l += m_ref == -INFINITY ? 1.f : ex2(b - m_ref);
+        }
         if (ok && n_blocks > 0) {
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&o_full[i]), 0))) {
                 if (lane == 0) fail(ERR_O_FULL);
@@ -399,7 +415,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         } else if (ok && n_blocks > 0) {
             tcgen05_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (kSink && extras.gate != nullptr)
+                inv *= 1.f / (1.f + __expf(-extras.gate[(int64_t)(q_begin + min(row, q_len - 1)) * extras.gate_stride + h0 + i]));
             bf16* orow = out + ((int64_t)(q_begin + min(row, q_len - 1)) * n_heads + h0 + i) * kD;
 #pragma unroll 1
             for (int c = 0; c < kD / 32; ++c) {
@@ -808,10 +826,12 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
 
 namespace fa5 {
 // out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M), M = max_s m_s, over the shares s of the keys;
-// with ``sink`` the denominator has one more term 2^(0 - M).
+// with ``sink`` the denominator has one more term 2^(b - M), b = 0 or the head's ``sinks`` entry in log2 units; with ``gate``
+// the row is multiplied by sigmoid(gate[token][head]).
 __global__ void combine_key_shares_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           bf16* __restrict__ out, int n_tokens, int n_heads, int D, int n_splits,
-                                          int sink) {
+                                          int sink, const float* __restrict__ sinks, const float* __restrict__ gate,
+                                          int64_t gate_stride) {
     const int64_t th = (int64_t)blockIdx.x * n_heads + blockIdx.y;
     const int64_t stride = (int64_t)n_tokens * n_heads;
     float mx = -INFINITY;
@@ -821,8 +841,9 @@ __global__ void combine_key_shares_kernel(const float* __restrict__ part_o, cons
         const float m = part_ml[2 * (s * stride + th)];
         if (m != -INFINITY) denom += part_ml[2 * (s * stride + th) + 1] * exp2f(m - mx);
     }
-    if (sink) denom += mx == -INFINITY ? 1.f : exp2f(-mx);
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    if (sink) denom += mx == -INFINITY ? 1.f : exp2f((sinks != nullptr ? sinks[blockIdx.y] * 1.4426950408889634f : 0.f) - mx);
+    float inv = denom > 0.f ? 1.f / denom : 0.f;
+    if (gate != nullptr) inv *= 1.f / (1.f + __expf(-gate[(int64_t)blockIdx.x * gate_stride + blockIdx.y]));
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s) {
@@ -837,7 +858,7 @@ template <int D, bool kSink = false>
 static int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_row,
                   int n_tiles, const int* cu_q, const int* kv_len, const int* slots, const int* page_table, int max_pages,
                   int n_tokens, int n_pages, int n_heads, int n_kv, float scale, float* scratch, int n_splits,
-                  cudaStream_t stream, int v_shift = 0, SinkExtras extras = SinkExtras{0, 0.f, 0.f, 0}) {
+                  cudaStream_t stream, int v_shift = 0, SinkExtras extras = SinkExtras{0, 0.f, 0.f, 0, 0, nullptr, nullptr, 0}) {
     CUtensorMap map_q, map_k, map_v;
     if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * D, (uint64_t)n_heads * D * 2, 64, kTileRows) ||
         !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, D, D * 2, 64, kPageTokens) ||
@@ -853,7 +874,9 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, void*
         part_o, part_ml, n_splits, n_tokens, v_shift, extras);
     if (n_splits > 1)
         combine_key_shares_kernel<<<dim3(n_tokens, n_heads), D / 2, 0, stream>>>(part_o, part_ml, (bf16*)out, n_tokens, n_heads,
-                                                                               D, n_splits, kSink ? extras.sink : 0);
+                                                                               D, n_splits, kSink ? extras.sink : 0,
+                                                                               kSink ? extras.sinks : nullptr,
+                                                                               kSink ? extras.gate : nullptr, extras.gate_stride);
     return launch_status();
 }
 }  // namespace fa5
@@ -899,20 +922,24 @@ CPM_API int cpm_prefill_attention_tcgen05_vshift(const void* q, const void* k_ca
                            n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, v_shift);
 }
 
-// Sink window attention of prompt tokens on the same kernel: keys 0 <= i - j < window (0: all), scores capped as
-// cap * tanh(s / cap) when cap > 0, one added to the softmax's denominator when sink != 0.  Sizes and scratch as above.
+// Sink window attention of prompt tokens on the same kernel: keys 0 <= i - j < window (0: all) and, with a window, the
+// sequence's first keep_first keys; scores capped as cap * tanh(s / cap) when cap > 0; with sink != 0 the softmax's
+// denominator has one more term exp(b_h), b_h = sinks[h] (fp32 [heads]) or 0 when sinks is null; with gate (fp32 rows of
+// gate_stride floats, one per head) head h's output is multiplied by sigmoid(gate[t][h]).  Sizes and scratch as above.
 CPM_API int cpm_sink_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
                                        const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
                                        const int* kv_len, const int* slots, const int* page_table, int max_pages,
                                        int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale, int window,
-                                       float cap, int sink, float* scratch, int n_splits, cudaStream_t stream) {
+                                       float cap, int sink, int keep_first, const float* sinks, const float* gate,
+                                       int64_t gate_stride, float* scratch, int n_splits, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
     if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !scratch) || n_tokens > 65535 * 1024) return CPM_BAD_ARGUMENT;
     if ((d != 128 && d != 64) || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
-        window < 0 || cap < 0.f || !(scale > 0.f) ||
+        window < 0 || keep_first < 0 || cap < 0.f || !(scale > 0.f) ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
         return CPM_BAD_ARGUMENT;
-    const fa5::SinkExtras extras{window, cap * 1.4426950408889634f, cap > 0.f ? scale / cap : 0.f, sink};
+    const fa5::SinkExtras extras{window, cap * 1.4426950408889634f, cap > 0.f ? scale / cap : 0.f, sink, keep_first, sinks, gate,
+                                 gate_stride};
     if (d == 128)
         return fa5::launch<128, true>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table,
                                       max_pages, n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream, 0, extras);

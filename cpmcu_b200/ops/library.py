@@ -85,7 +85,7 @@ _SIGNATURES = {
                                 c_int, c_float, c_float, c_int, _P, _P, c_int64, _P, c_int, _P],
     "cpm_sink_attention_bf16_sizes": [c_int, c_int],
     "cpm_sink_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_float, c_int, c_float, c_int, _P, c_int, _P],
+                                   c_float, c_int, c_float, c_int, c_int, _P, _P, c_int64, _P, c_int, _P],
     "cpm_talking_attention": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_scale_heads_bf16": [_P, _P, _P, c_int, c_int, c_int, _P],
     "cpm_talk_mix_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],

@@ -978,10 +978,8 @@ class Ops:
                 and os.environ.get("CPMCU_SINK_GENERIC", "0") != "1"):
             if (not ctx.is_decode and ctx.q_tiles is not None and ctx.max_q_len >= self.SINK_TCGEN05_MIN_ROWS
                     and self.use_tcgen05_attention and self.use_tcgen05_sink and d == dv and (n_heads // n_kv) % 2 == 0
-                    and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024)) and not (keep_first and window)
-                    and sinks is None):
-                out = self.sink_attention_tcgen05(ctx, q, lane, n_kv, scale, window, cap, sink)
-                return out if gate is None else self.head_gate(out, gate, n_heads)
+                    and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024))):
+                return self.sink_attention_tcgen05(ctx, q, lane, n_kv, scale, window, cap, sink, keep_first, sinks, gate)
             return self.sink_attention_bf16(ctx, q, lane, n_kv, dv, scale, window, cap, sink, keep_first, sinks, gate)
         return self.sink_attention_generic(ctx, q, lane, n_kv, dv, scale, window, cap, sink, keep_first, sinks, gate)
 
@@ -998,22 +996,24 @@ class Ops:
     SINK_TCGEN05_MIN_ROWS = 32   # prompt portions from this many tokens on take the tcgen05 kernel's 128-row tiles
 
     def sink_attention_tcgen05(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, window: int, cap: float,
-                               sink: bool) -> torch.Tensor:
+                               sink: bool, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                               gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Prompt tokens on the tcgen05 kernel of ``prefill_attention_tcgen05`` (equal key and value head sizes of 128 or
         64, an even number of query heads per key-value head): the window moves a tile's first key step and masks its
         edge, the cap and the sink join the softmax threads' work.  The weights enter the second product as bf16."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = ctx.q_tiles
+        keep, p_sinks, p_gate, gate_stride = self._sink_extras(n, n_heads, window, keep_first, sinks, gate)
         out = self.empty(n, n_heads * d)
-        keys = min(ctx.max_kv_len, int(window) + 128) if window else ctx.max_kv_len
+        keys = min(ctx.max_kv_len, int(window) + 128 + keep) if window else ctx.max_kv_len
         n_splits = self.prefill_key_shares(ctx.q_lens, keys, n_heads)
         scratch = self.empty(n_splits * n * n_heads * (d + 2), dtype=torch.float32) if n_splits > 1 else None
         check(self.lib.cpm_sink_attention_tcgen05(_ptr(q), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(tile_seq), _ptr(tile_row),
                                                   int(n_tiles), _ptr(ctx.cu_q), _ptr(ctx.kv_len_dev), _ptr(ctx.slot_dev),
                                                   _ptr(lane.page_table), lane.page_table.shape[1], n, lane.k.shape[0], n_heads,
-                                                  n_kv, d, float(scale), int(window), float(cap), 1 if sink else 0,
-                                                  _ptr(scratch), n_splits, self._stream()),
+                                                  n_kv, d, float(scale), int(window), float(cap), 1 if sink else 0, keep, p_sinks,
+                                                  p_gate, gate_stride, _ptr(scratch), n_splits, self._stream()),
               f"tcgen05 sink attention (head_dim {d})")
         return out
 
