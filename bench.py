@@ -1223,6 +1223,285 @@ def workload_kipizen(steps: int, warmup: int, size: str, batch: int) -> int:
     return 0
 
 
+# Lukelorn at the sizes of MUFEVIK_SIZES beside Kipizen at the same sizes (the closest design: window attention with capped
+# scores and a sink, a matrix-state recurrence, routed experts): eight parallel layers (delta rule with a decay per key
+# channel, window attention that keeps first tokens, the same layer's tensors once more with a cache of its own, latent
+# attention with a rotated key part, ...); random weights N(0, 0.02), vectors N(0, 0.02) around their neutral value.
+LUKELORN_WINDOW, LUKELORN_KEEP = 1024, 64
+LUKELORN_LATENT = {"1k": dict(q_rank=384, kv_rank=192, rot_dim=32), "2k": dict(q_rank=768, kv_rank=448, rot_dim=64)}
+
+
+def lukelorn_config(z: dict, lat: dict) -> dict:
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]}}
+    dense = {"kind": "dense", "ff": z["ff"] * z["top"]}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                     "softcap": 30.0, "mask": {"size": LUKELORN_WINDOW, "keep_first": LUKELORN_KEEP},
+                     "rot": {"dims": z["dim"], "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    delta = {"type": "channel_delta", "mlp": moe,
+             "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_qk_heads"], "dim": z["delta_dim"], "vdim": z["delta_vdim"],
+                       "conv": z["conv"], "decay_rank": 32, "gate_rank": 32}}
+    latent = {"type": "latent_attention", "mlp": dense,
+              "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": lat["rot_dim"], "vdim": z["vdim"], "q_rank": lat["q_rank"],
+                        "kv_rank": lat["kv_rank"], "scale": (z["dim"] + lat["rot_dim"]) ** -0.5, "mask": {"size": LUKELORN_WINDOW},
+                        "rot": {"dims": lat["rot_dim"], "base": 10000.0}}}
+    return {"architecture": "Lukelorn", "vocab": z["vocab"], "width": z["width"], "residual_mult": 0.5, "norm": {"eps": 1e-5},
+            "layers": [delta, att, dict(att, weights_of=1), latent, delta, att, dict(att, weights_of=5), latent]}
+
+
+def build_lukelorn(z: dict, lat: dict, max_tokens: int, max_batch: int, context: int):
+    import torch
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.storage import make_storage
+    from cpmcu_b200.loading import build_model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import random_tensors
+
+    arch = architecture("Lukelorn")
+    cfg = arch.config_class.from_dict(lukelorn_config(z, lat))
+    model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
+    storage = make_storage(model, PREFILL_TOKENS, max_batch, max_tokens=max_tokens, max_seq_tokens=context + 64, n_slots=max_batch + 2)
+    tensors = random_tensors(model.weight_specs(), 7, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0")
+    for name, t in tensors.items():
+        if name.endswith(("norm1", "final.norm", ".sink")):
+            t.sub_(1.0)                                   # stored around zero
+        elif name.endswith((".conv", ".A_log", ".dt_bias")):
+            t.mul_(0.3)
+    model.load_weights(tensors)
+    del tensors
+    torch.cuda.empty_cache()
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=PREFILL_TOKENS, graph_prompts=True)
+
+
+def lukelorn_kernels(z: dict, lat: dict, pk: dict, context: int, batch: int) -> dict:
+    """Every kernel of the design alone, at the size's shapes, beside the like kernel of the closest models (Kipizen's
+    window attention and its preparation, Mufevik's delta rule with a decay per head, Reravik's latent attention over a
+    row of equal size, the gated experts): a prompt of 2,048 tokens and a decode step of ``batch`` sequences at
+    ``context`` tokens.  CUDA events around one launch after a flush of L2 (a 512 MB buffer is written), median of five;
+    bytes and FLOPs are the algorithmic ones (attention: the keys a window holds and the kept first tokens)."""
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import Ops
+    from cpmcu_b200.parts.base import CacheNeeds, QUERY_TILE_TOKENS, StepContext
+
+    ops = Ops(torch.bfloat16)
+    dev = "cuda:0"
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    W, H, G, d, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    T, win, keep = PREFILL_TOKENS, LUKELORN_WINDOW, LUKELORN_KEEP
+    i32 = dict(dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for _ in range(6):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[1:])
+
+    def context_of(q_lens, starts, slots):
+        pos = torch.cat([torch.arange(s, s + n) for n, s in zip(q_lens, starts)]).to(**i32)
+        seq = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(**i32)
+        cu = torch.tensor([0] + [sum(q_lens[:i + 1]) for i in range(len(q_lens))], **i32)
+        kv = [s + n for n, s in zip(q_lens, starts)]
+        ctx = StepContext(n_tokens=sum(q_lens), n_seqs=len(q_lens), is_decode=all(n == 1 for n in q_lens), captured=False,
+                          q_lens=list(q_lens), kv_lens=kv, slots=list(slots), max_q_len=max(q_lens), max_kv_len=max(kv),
+                          token_ids=torch.zeros(sum(q_lens), **i32), positions=pos, token_seq=seq, cu_q=cu,
+                          kv_len_dev=torch.tensor(kv, **i32), slot_dev=torch.tensor(list(slots), **i32))
+        ts = [i for i, n in enumerate(q_lens) for _ in range(0, n, QUERY_TILE_TOKENS)]
+        tr = [r for n in q_lens for r in range(0, n, QUERY_TILE_TOKENS)]
+        ctx.q_tiles = (torch.tensor(ts, **i32), torch.tensor(tr, **i32), len(ts))
+        return ctx
+
+    out = {}
+
+    def note(name, ms, nbytes=0.0, flops=0.0, like=None):
+        row = {"us": ms * 1e3}
+        if nbytes:
+            row["gbs"] = nbytes / (ms * 1e-3) / 1e9
+            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
+        if flops:
+            row["tflops"] = flops / (ms * 1e-3) / 1e12
+            row["frac_bf16"] = row["tflops"] / pk["bf16_tflops"]
+        if like:
+            row["like"] = like
+        out[name] = row
+
+    n_slots = batch + 2
+    R, QR, dr = lat["kv_rank"], lat["q_rank"], lat["rot_dim"]
+    row = R + dr
+    cache = Cache([CacheNeeds(kv_heads=G, head_dim=d, value_dim=dv if dv != d else 0),
+                   CacheNeeds(kv_heads=1, head_dim=row, values=False)], max_tokens=(batch + 1) * (context + 64),
+                  dtype=torch.bfloat16, device=dev, n_slots=n_slots)
+    slots = [cache.open_sequence() for _ in range(batch)]
+    for s_ in slots:
+        cache.reserve(s_, context)
+    cache.sync()
+    lane, llane = cache.lane(0), cache.lane(1)
+    lane.k.normal_(0, 0.5)
+    lane.v.normal_(0, 0.5)
+    llane.k.normal_(0, 0.5)
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    DH, DG, dd, ddv, K = z["delta_heads"], z["delta_qk_heads"], z["delta_dim"], z["delta_vdim"], z["conv"]
+    wg = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wu = torch.randn(E, ff, W, device=dev).bfloat16() * 0.02
+    wd = torch.randn(E, W, ff, device=dev).bfloat16() * 0.02
+    for phase, q_lens, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx = context_of(q_lens, starts, slots[:len(q_lens)])
+        n = ctx.n_tokens
+        keys = [s + j + 1 for nq, s in zip(q_lens, starts) for j in range(nq)]
+        seen = [min(k_, win + keep) for k_ in keys]
+        seen_plain = [min(k_, win) for k_ in keys]
+        # window attention: the preparation (adjacent pairs, no bias, no unit length) and the attention with kept first
+        # tokens, learned sinks and the gate in its last step, beside the forms Kipizen runs
+        cols = (H + G) * d + G * dv
+        proj = torch.randn(n, cols + H, device=dev)
+        inv = torch.ones(d // 2, device=dev)
+        note(f"{phase}/qk_prepare_store (rotation of adjacent pairs, store)",
+             timed(lambda: ops.qk_prepare_store(ctx, proj, lane, H, G, d, dv, (None, None, None), inv, d, False, 0.0, adjacent=True,
+                                                extra_cols=H)), n * cols * 6.0, like="qk_prepare_store (Kipizen)")
+        projk = torch.randn(n, cols, device=dev)
+        bq, bk, bv = torch.zeros(H * d, device=dev), torch.zeros(G * d, device=dev), torch.zeros(G * dv, device=dev)
+        inv4 = torch.ones(d // 4, device=dev)
+        note(f"{phase}/qk_prepare_store (Kipizen: bias, rotation of half a head, unit rms, store)",
+             timed(lambda: ops.qk_prepare_store(ctx, projk, lane, H, G, d, dv, (bq, bk, bv), inv4, d // 2, True, 1e-5)), n * cols * 6.0)
+        lane.k.normal_(0, 0.5)
+        q = torch.randn(n, H, d, device=dev).bfloat16()
+        sinks = torch.randn(H, device=dev)
+        gate = proj[:, cols:]
+        note(f"{phase}/sink_attention (window {win}, {keep} kept first tokens, cap, learned sinks, gate)",
+             timed(lambda: ops.sink_attention(ctx, q, lane, G, dv, d ** -0.5, win, 30.0, True, keep_first=keep, sinks=sinks, gate=gate)),
+             nbytes=(len(q_lens) * min(context, win + keep) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
+             flops=2.0 * H * (d + dv) * sum(seen), like="sink_attention (Kipizen)")
+        note(f"{phase}/sink_attention (Kipizen: window {win}, cap, sink of score 0)",
+             timed(lambda: ops.sink_attention(ctx, q, lane, G, dv, d ** -0.5, win, 30.0, True)),
+             nbytes=(len(q_lens) * min(context, win) * G * (d + dv) * 2.0) if phase == "decode" else 0.0,
+             flops=2.0 * H * (d + dv) * sum(seen_plain))
+        # the delta rule with a decay per key channel beside Mufevik's with a decay per head
+        C = 2 * DG * dd + DH * ddv
+        dproj = torch.randn(n, C + 2 * DH + 64, device=dev)
+        taps = torch.randn(C, K, device=dev) * 0.3
+        cstate = torch.zeros(n_slots, max(K - 1, 1), C, device=dev)
+        al, db, dbc = torch.zeros(DH, device=dev), torch.zeros(DH, device=dev), torch.zeros(DH * dd, device=dev)
+        note(f"{phase}/conv_prepare (no decay)",
+             timed(lambda: ops.conv_prepare(ctx, dproj, taps, cstate, al, db, C, 0, DH, DG, dd, ddv, 1e-6, head_decay=False)),
+             n * C * 8.0, like="conv_prepare (Mufevik)")
+        note(f"{phase}/conv_prepare (Mufevik: with the decay per head)",
+             timed(lambda: ops.conv_prepare(ctx, dproj, taps, cstate, al, db, C, C + DH, DH, DG, dd, ddv, 1e-6)), n * C * 8.0)
+        zlog = torch.randn(n, DH * dd, device=dev)
+        note(f"{phase}/channel_decay", timed(lambda: ops.channel_decay(zlog, al, dbc, DH, dd)), n * DH * dd * 8.0, like="sigmoid_power (Mufevik)")
+        note(f"{phase}/sigmoid_power (Mufevik)", timed(lambda: ops.sigmoid_power(zlog, dbc, 8.0)), n * DH * dd * 8.0)
+        qd, kd, vd_, beta, hdecay = ops.conv_prepare(ctx, dproj, taps, cstate, al, db, C, C + DH, DH, DG, dd, ddv, 1e-6)
+        cdecay = torch.rand(n, DH * dd, device=dev) * 0.1 + 0.9
+        dstate = torch.zeros(n_slots, DH, dd, ddv, device=dev)
+        rec_bytes = len(q_lens) * DH * dd * ddv * 8.0 + n * (2 * DG * dd + DH * ddv + DH * ddv) * 4.0
+        note(f"{phase}/linear_recurrence (delta rule, decay per key channel)",
+             timed(lambda: ops.linear_recurrence(ctx, qd, kd, vd_, cdecay, beta, dstate, DH, DG, dd, ddv, dd ** -0.5, vector_decay=True)),
+             nbytes=rec_bytes + n * DH * dd * 4.0, flops=6.0 * n * DH * dd * ddv, like="linear_recurrence (Mufevik)")
+        note(f"{phase}/linear_recurrence (Mufevik: delta rule, decay per head)",
+             timed(lambda: ops.linear_recurrence(ctx, qd, kd, vd_, hdecay, beta, dstate, DH, DG, dd, ddv, dd ** -0.5)),
+             nbytes=rec_bytes, flops=6.0 * n * DH * dd * ddv)
+        o = torch.randn(n, DH, ddv, device=dev)
+        og = torch.randn(n, DH * ddv, device=dev)
+        wv = torch.ones(ddv, device=dev)
+        note(f"{phase}/gated_head_norm (sigmoid gate)", timed(lambda: ops.gated_head_norm(o, og, wv, 1e-5, "sigmoid")),
+             n * DH * ddv * 10.0, like="gated_head_norm (Mufevik)")
+        note(f"{phase}/gated_head_norm (Mufevik)", timed(lambda: ops.gated_head_norm(o, og, wv, 1e-5)), n * DH * ddv * 10.0)
+        # latent attention with a rotated key part beside Reravik's over a row of equal size
+        down = torch.randn(n, QR + row + H, device=dev)
+        gq, gkv, invr = torch.ones(QR, device=dev), torch.ones(R, device=dev), torch.ones(max(dr // 2, 1), device=dev)
+        note(f"{phase}/latent_norm_store (with the rotated key part)",
+             timed(lambda: ops.latent_norm_store(ctx, down, gq, gkv, llane, QR, R, 1e-5, rot_dim=dr, inv_freq=invr, adjacent=True)),
+             n * (QR + row) * 6.0, like="latent_norm_store (Reravik)")
+        note(f"{phase}/latent_norm_store (Reravik: a row of {row} values)",
+             timed(lambda: ops.latent_norm_store(ctx, down, gq, gkv, llane, QR, row, 1e-5)), n * (QR + row) * 6.0)
+        llane.k.normal_(0, 0.5)
+        qf = torch.randn(n, H * (d + dr), device=dev)
+        note(f"{phase}/rotate_heads", timed(lambda: ops.rotate_heads(ctx, qf, H, d, dr, invr, True)), n * H * (d + dr) * 6.0,
+             like="rope_store_dv (Mufevik)")
+        qkv = torch.randn(n, cols, device=dev).bfloat16()
+        note(f"{phase}/rope_store_dv (Mufevik)", timed(lambda: ops.rope_store_dv(ctx, qkv, lane, H, G, d, dv, inv, d)), n * cols * 4.0)
+        lane.k.normal_(0, 0.5)
+        q_lat = torch.randn(n, H, row, device=dev)
+        lkeys = [min(k_, win) for k_ in keys]
+        note(f"{phase}/latent_attention (row {row} = rank {R} + rotated {dr}, window {win})",
+             timed(lambda: ops.latent_attention(ctx, q_lat, llane, (d + dr) ** -0.5, win, out_compute_dtype=True)),
+             nbytes=(len(q_lens) * min(context, win) * row * 2.0) if phase == "decode" else 0.0,
+             flops=4.0 * H * row * sum(lkeys), like="the same kernel (Reravik's rows hold the latent alone)")
+        oh = torch.randn(n, H * dv, device=dev).bfloat16()
+        note(f"{phase}/head_gate", timed(lambda: ops.head_gate(oh, down[:, QR + row:], H)), n * H * dv * 4.0, like="silu_columns (Kipizen)")
+        sc = torch.randn(n, H * dv, device=dev)
+        note(f"{phase}/silu_columns (Kipizen)", timed(lambda: ops.silu_columns(sc, H * dv)), n * H * dv * 8.0)
+        # the residual and norm, and the experts
+        x1 = torch.randn(n, W, device=dev)
+        y = torch.randn(n, W, device=dev).bfloat16()
+        wn = torch.ones(W, device=dev)
+        note(f"{phase}/add_rmsnorm (32-bit residual, weight 1 + w)", timed(lambda: ops.add_rmsnorm(x1, y, 0.5, wn, 1e-5)), n * W * 12.0)
+        logits = torch.randn(n, E, device=dev)
+        rb = torch.zeros(E, device=dev)
+        note(f"{phase}/moe_route (sigmoid scores)", timed(lambda: ops.moe_route(logits, None, E, top, 1, 1, sigmoid=True)), n * E * 4.0,
+             like="moe_route (Kipizen)")
+        note(f"{phase}/moe_route (Kipizen: largest logits, softmax over the chosen)",
+             timed(lambda: ops.moe_route(logits, None, E, top, 1, 1, bias=rb, top_first=True)), n * E * 4.0)
+        chosen, weights, _ = ops.moe_route(logits, None, E, top, 1, 1, sigmoid=True)
+        used = int(torch.unique(chosen).numel())
+        note(f"{phase}/moe_experts (up, relu squared, down; the weight on the input)",
+             timed(lambda: ops.moe_experts(y, chosen, None, wu, wd, input_scale=weights)),
+             nbytes=used * 2.0 * ff * W * 2.0 + n * top * (W + ff) * 4.0, flops=4.0 * n * top * ff * W, like="moe_experts (Kipizen)")
+        note(f"{phase}/moe_experts (Kipizen: gate, up, down)", timed(lambda: ops.moe_experts(y, chosen, wg, wu, wd)),
+             nbytes=used * 3.0 * ff * W * 2.0 + n * top * (W + ff) * 4.0, flops=6.0 * n * top * ff * W)
+        pairs = ops.moe_experts(y, chosen, None, wu, wd, input_scale=weights)
+        note(f"{phase}/moe_combine (plain sum)", timed(lambda: ops.moe_combine(pairs, None, None, None, top=top)), n * W * 2.0 * (top + 1),
+             like="moe_combine (Kipizen)")
+        note(f"{phase}/moe_combine (Kipizen: weighted)", timed(lambda: ops.moe_combine(pairs, weights, None, None)), n * W * 2.0 * (top + 1))
+    return out
+
+
+def workload_lukelorn(steps: int, warmup: int, size: str, batch: int) -> int:
+    """Lukelorn at one of MUFEVIK_SIZES beside Kipizen at the same sizes (the closest design): decode steps of ``batch``
+    sequences ending at a context of 4,096 tokens under a CUDA graph, a prompt of 2,048 tokens, and every kernel of the
+    design alone beside its like."""
+    import torch
+
+    z, lat, pk, context = MUFEVIK_SIZES[size], LUKELORN_LATENT[size], peaks(), CONTEXT
+    cfg, model, cache, stepper = build_lukelorn(z, lat, batch * (context + 64) + 128, batch, context)
+    pre_ms = time_prefill_any(stepper, cfg.vocab)
+    ms, clocks, launches, cache_bytes = time_decode(stepper, batch, steps, warmup, cfg.vocab, True, context=context)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    del model, cache, stepper
+    torch.cuda.empty_cache()
+    kcfg, kmodel, kcache, kstepper = build_kipizen(z, batch * (context + 64) + 128, batch, context)
+    k_pre = time_prefill_any(kstepper, kcfg.vocab)
+    k_ms, _, k_launches, k_cache = time_decode(kstepper, batch, steps, warmup, kcfg.vocab, False, context=context)
+    k_weights = kmodel.weight_bytes_per_step()
+    k_achieved = (k_weights + k_cache) / (k_ms * 1e-3) / 1e9
+    del kmodel, kcache, kstepper
+    torch.cuda.empty_cache()
+    kernels = lukelorn_kernels(z, lat, pk, context, batch)
+    print(json.dumps({
+        "workload": "lukelorn", "metric": f"decode tokens/s (Lukelorn {size} sizes, bf16, batch {batch}, context {context})",
+        "value": batch * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 7",
+        "config": dict(z, **lat, size=size, layers=len(cfg.layers), window=LUKELORN_WINDOW, keep_first=LUKELORN_KEEP,
+                       global_batch=batch, seq_len=context, prefill_tokens=PREFILL_TOKENS, cuda_graph=True, peaks=pk["source"]),
+        "prefill": {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "ms": pre_ms},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "weight_bytes": weight_bytes, "cache_bytes": cache_bytes},
+        "closest_model": {"model": f"Kipizen at the {size} sizes, {len(kcfg.layers)} layers",
+                          "decode_tokens_s": batch * 1000.0 / k_ms, "ms_per_step": k_ms, "prefill_tokens_s": PREFILL_TOKENS / (k_pre * 1e-3),
+                          "prefill_ms": k_pre, "roofline_frac": k_achieved / pk["hbm_gbs"], "weight_bytes": k_weights,
+                          "cache_bytes": k_cache, "gpu_launches": k_launches},
+        "kernels": kernels, "clocks": clocks, "gpu_launches": launches,
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1231,12 +1510,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik", "mufevik", "kipizen"],
+    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b", "reravik", "mufevik", "kipizen", "lukelorn"],
                     help="dense8b: the headline line (8B sizes, batch 8, context 4096); half_b: 0.5B sizes, batch 64, prompts "
                          "uniform in [64, 2048] chunked at 512, decode at context 8192 (256 steps by default); sparse8b: 8B "
                          "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps; reravik: the Reravik "
                          "design at --size beside MiniCPM4 of equal sizes, and its kernels alone; mufevik: the same for the Mufevik design "
-                         "(sizes 1k and 2k); kipizen: the Kipizen design beside Mufevik at the same sizes (1k and 2k), and its kernels alone")
+                         "(sizes 1k and 2k); kipizen: the Kipizen design beside Mufevik at the same sizes (1k and 2k), and its kernels alone; "
+                         "lukelorn: the Lukelorn design beside Kipizen at the same sizes (1k and 2k), and its kernels alone")
     ap.add_argument("--size", default="2k", choices=sorted(RERAVIK_SIZES), help="--workload reravik / mufevik: which layer sizes")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
     ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
@@ -1269,6 +1549,11 @@ def main() -> int:
             print(f"bench.py: --workload kipizen takes --size {' or '.join(sorted(MUFEVIK_SIZES))}")
             return 2
         return workload_kipizen(a.steps, max(3, a.warmup), a.size, a.batch)
+    if a.workload == "lukelorn":
+        if a.size not in MUFEVIK_SIZES:
+            print(f"bench.py: --workload lukelorn takes --size {' or '.join(sorted(MUFEVIK_SIZES))}")
+            return 2
+        return workload_lukelorn(a.steps, max(3, a.warmup), a.size, a.batch)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)

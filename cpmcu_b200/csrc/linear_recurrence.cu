@@ -424,12 +424,13 @@ CPM_API int cpm_sigmoid_power(float* z, const float* bias, float tau, int n_toke
     return launch_status();
 }
 
-// out[t][h][:] = o[t][h][:] / sqrt(mean(o^2) + eps) * weight[:] * silu(gate[t][h][:]), one warp per (token, head);
+// out[t][h][:] = o[t][h][:] / sqrt(mean(o^2) + eps) * weight[:] * act(gate[t][h][:]), act = SiLU or (gate_act 1) the
+// sigmoid, one warp per (token, head);
 // o fp32 [tokens, heads, dv], gate fp32 rows of ``gate_stride`` floats holding [heads, dv], out in the storage type.
 template <typename T>
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t gate_stride,
                                        const float* __restrict__ weight, T* __restrict__ out, int heads, int dv, float eps,
-                                       int64_t n_units) {
+                                       int64_t n_units, int gate_act) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -442,22 +443,23 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const float*
     for (int c = lane; c < dv; c += 32) ss = fmaf(row[c], row[c], ss);
     const float f = rsqrtf(warp_sum(ss) / (float)dv + eps);
     const float* gr = gate + t * gate_stride + (int64_t)h * dv;
-    for (int c = lane; c < dv; c += 32) out[w * dv + c] = from_f32<T>(row[c] * f * weight[c] * silu_acc(gr[c]));
+    for (int c = lane; c < dv; c += 32)
+        out[w * dv + c] = from_f32<T>(row[c] * f * weight[c] * (gate_act == 1 ? sigmoid_acc(gr[c]) : silu_acc(gr[c])));
 }
 
 CPM_API int cpm_gated_head_norm(const float* o, const float* gate, int64_t gate_stride, const float* weight, void* out,
-                                int n_tokens, int heads, int dv, float eps, int dtype, cudaStream_t stream) {
+                                int n_tokens, int heads, int dv, float eps, int gate_act, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    if (heads < 1 || dv < 1) return CPM_BAD_ARGUMENT;
+    if (heads < 1 || dv < 1 || gate_act < 0 || gate_act > 1) return CPM_BAD_ARGUMENT;
     const int64_t units = (int64_t)n_tokens * heads;
     const int warps = 8;
     const dim3 grid((unsigned)((units + warps - 1) / warps));
     if (dtype == CPM_BF16)
         cpm_launch(kLaunchNorm, gated_head_norm_kernel<bf16>, grid, dim3(warps * 32), 0, stream, o, gate, gate_stride, weight, (bf16*)out,
-                   heads, dv, eps, units);
+                   heads, dv, eps, units, gate_act);
     else
         cpm_launch(kLaunchNorm, gated_head_norm_kernel<float>, grid, dim3(warps * 32), 0, stream, o, gate, gate_stride, weight,
-                   (float*)out, heads, dv, eps, units);
+                   (float*)out, heads, dv, eps, units, gate_act);
     return launch_status();
 }
 

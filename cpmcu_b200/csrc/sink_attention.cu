@@ -732,11 +732,35 @@ __global__ void head_gate_kernel(T* __restrict__ x, const float* __restrict__ ga
     x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-z)));
 }
 
+// The same for bf16 heads of a multiple of 8 channels: a thread takes 8 channels of one head (16-byte accesses).
+__global__ void head_gate_bf16x8_kernel(bf16* __restrict__ x, const float* __restrict__ gate, int64_t gate_stride, int64_t n_vec,
+                                        int n_heads, int vec_per_head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int64_t th = i / vec_per_head;
+    const float f = 1.0f / (1.0f + expf(-gate[(th / n_heads) * gate_stride + th % n_heads]));
+    uint4 v = *reinterpret_cast<const uint4*>(x + i * 8);
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(p[j]);
+        p[j] = __floats2bfloat162_rn(a.x * f, a.y * f);
+    }
+    *reinterpret_cast<uint4*>(x + i * 8) = v;
+}
+
 CPM_API int cpm_head_gate(void* x, const float* gate, int64_t gate_stride, int n_tokens, int n_heads, int dv, int dtype,
                           cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (n_heads < 1 || dv < 1 || !gate) return CPM_BAD_ARGUMENT;
     const int64_t n = (int64_t)n_tokens * n_heads * dv;
+    if (dtype == CPM_BF16 && dv % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+        cpm_launch(kLaunchOther, head_gate_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (bf16*)x, gate,
+                   gate_stride, n / 8, n_heads, dv / 8);
+        return launch_status();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == CPM_BF16)
         cpm_launch(kLaunchOther, head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, gate, gate_stride, n, n_heads, dv);

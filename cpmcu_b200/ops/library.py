@@ -73,7 +73,7 @@ _SIGNATURES = {
     "cpm_conv_prepare": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_float, _P],
     "cpm_sigmoid_power": [_P, _P, c_float, c_int, c_int, _P],
-    "cpm_gated_head_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "cpm_gated_head_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
     "cpm_dual_rmsnorm_mean": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "cpm_gated_group_norm": [_P, _P, c_int64, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_silu_columns": [_P, c_int64, c_int, c_int, _P],

@@ -894,9 +894,10 @@ class Ops:
         check(self.lib.cpm_sigmoid_power(_ptr(z), _ptr(bias), float(tau), z.shape[0], z.shape[1], self._stream()), "sigmoid_power")
         return z
 
-    def gated_head_norm(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    def gated_head_norm(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float,
+                        gate_activation: str = "silu") -> torch.Tensor:
         """o fp32 [tokens, heads, dv], gate fp32 [tokens, heads*dv] (may be a slice of wider rows), weight fp32 [dv] ->
-        rms_norm(o) * weight * silu(gate) per head, [tokens, heads*dv] in the compute dtype."""
+        rms_norm(o) * weight * act(gate) per head (act: "silu" or "sigmoid"), [tokens, heads*dv] in the compute dtype."""
         self._f32(o, "recurrence output")
         self._f32(weight, "head norm weight")
         n, heads, dv = o.shape
@@ -904,7 +905,7 @@ class Ops:
             raise ValueError("gated_head_norm: the gate must be fp32 [tokens, heads*dv]")
         out = self.empty(n, heads * dv)
         check(self.lib.cpm_gated_head_norm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), n, heads, dv, float(eps),
-                                           self.code, self._stream()), "gated_head_norm")
+                                           {"silu": 0, "sigmoid": 1}[gate_activation], self.code, self._stream()), "gated_head_norm")
         return out
 
     GATE_ACTIVATIONS = {"silu": 0, "sigmoid": 1}

@@ -196,9 +196,7 @@ class GatedDeltaRule(_MatrixStateMixer):
             gate = ops.linear(self._narrow(proj, col["g1"], self.gate_rank), self.w_g2, out_f32=True)
         else:
             gate = proj[:, col["g"]:col["g"] + H * dv]
-        if self.gate == "silu":
-            return ops.linear(ops.gated_head_norm(o, gate, self.w_norm, self.eps), self.w_o)
-        return ops.linear(ops.gated_group_norm(o, gate, self.w_norm, self.eps, 1, self.gate), self.w_o)
+        return ops.linear(ops.gated_head_norm(o, gate, self.w_norm, self.eps, self.gate), self.w_o)
 
     def _narrow(self, proj: torch.Tensor, first: int, width: int) -> torch.Tensor:
         """Columns of the fused product as a contiguous operand of the next product (compute dtype)."""
