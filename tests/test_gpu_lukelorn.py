@@ -339,9 +339,9 @@ def _tower_data(T, H, G, d, dv, window, keep, seed):
 
 ATTENTION_SIZES = [
     # H, G, d, dv, window, keep_first, cap
-    (6, 3, 128, 128, 70, 9, 20.0), (8, 2, 64, 32, 64, 64, 0.0), (4, 1, 32, 96, None, 0, 7.0), (34, 2, 32, 32, 1, 1, 0.0),
+    (6, 2, 128, 128, 70, 9, 18.0), (8, 2, 64, 32, 64, 64, 0.0), (4, 1, 32, 96, None, 0, 7.0), (34, 2, 32, 32, 1, 1, 0.0),
     (3, 3, 96, 64, 33, 65, 30.0), (5, 5, 12, 36, 129, 2, 15.0), (4, 2, 24, 40, 40, 130, 0.0), (2, 1, 200, 130, 65, 3, 50.0),
-    (16, 1, 64, 128, 100, 33, 25.0), (2, 2, 128, 64, 2, 70, 0.0), (4, 2, 64, 64, 96, 0, 10.0),
+    (16, 1, 64, 128, 100, 33, 25.0), (2, 2, 128, 64, 2, 70, 0.0), (4, 2, 64, 64, 90, 0, 10.0),
 ]
 
 
