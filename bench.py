@@ -1441,7 +1441,10 @@ def lukelorn_kernels(z: dict, lat: dict, pk: dict, context: int, batch: int) -> 
         x1 = torch.randn(n, W, device=dev)
         y = torch.randn(n, W, device=dev).bfloat16()
         wn = torch.ones(W, device=dev)
-        note(f"{phase}/add_rmsnorm (32-bit residual, weight 1 + w)", timed(lambda: ops.add_rmsnorm(x1, y, 0.5, wn, 1e-5)), n * W * 12.0)
+        y2 = torch.randn(n, W, device=dev).bfloat16()
+        note(f"{phase}/add_rmsnorm (32-bit residual, the two sublayers' outputs added in one pass)",
+             timed(lambda: ops.add_rmsnorm(x1, y, 0.5, wn, 1e-5, delta2=y2)), n * W * 14.0, like="add_rmsnorm (Kipizen)")
+        note(f"{phase}/add_rmsnorm (Kipizen: one output added)", timed(lambda: ops.add_rmsnorm(x1, y, 1.0, wn, 1e-5)), n * W * 12.0)
         logits = torch.randn(n, E, device=dev)
         rb = torch.zeros(E, device=dev)
         note(f"{phase}/moe_route (sigmoid scores)", timed(lambda: ops.moe_route(logits, None, E, top, 1, 1, sigmoid=True)), n * E * 4.0,

@@ -64,7 +64,7 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 }
 
 template <typename T, typename W>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, float alpha,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ delta2, float alpha,
                                    const W* __restrict__ w, T* __restrict__ y,
                                    const int* __restrict__ rows, int hidden, float eps, int write_back) {
     extern __shared__ float row_cache[];   // hidden floats + 33
@@ -74,6 +74,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     const int64_t src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + src_row * hidden;
     const T* dr = delta ? delta + src_row * hidden : nullptr;
+    const T* dr2 = (delta && delta2) ? delta2 + src_row * hidden : nullptr;      // a second addend with the same factor
     float ss = 0.f;
     if ((hidden & 3) == 0) {
         // four elements per thread and step: 16-byte loads of the fp32 stream, one load of the addend's four
@@ -85,6 +86,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                 v.y = fmaf(alpha, d4.y, v.y);
                 v.z = fmaf(alpha, d4.z, v.z);
                 v.w = fmaf(alpha, d4.w, v.w);
+                if (dr2) {
+                    const float4 e4 = load4(dr2 + c);
+                    v.x = fmaf(alpha, e4.x, v.x);
+                    v.y = fmaf(alpha, e4.y, v.y);
+                    v.z = fmaf(alpha, e4.z, v.z);
+                    v.w = fmaf(alpha, e4.w, v.w);
+                }
                 if (write_back) *reinterpret_cast<float4*>(xr + c) = v;
             }
             *reinterpret_cast<float4*>(row_cache + c) = v;
@@ -95,6 +103,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
             float v = xr[c];
             if (dr) {
                 v = fmaf(alpha, to_f32(dr[c]), v);
+                if (dr2) v = fmaf(alpha, to_f32(dr2[c]), v);
                 if (write_back) xr[c] = v;
             }
             row_cache[c] = v;
@@ -117,7 +126,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 }
 
 template <typename T, typename W>
-static int launch_add_rmsnorm(float* x, const void* delta, float alpha, const void* w, void* y, const int* rows,
+static int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, float alpha, const void* w, void* y, const int* rows,
                               int n_rows, int hidden, float eps, int write_back, cudaStream_t stream) {
     const size_t smem = (size_t)(hidden + 33) * sizeof(float);
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
@@ -127,20 +136,21 @@ static int launch_add_rmsnorm(float* x, const void* delta, float alpha, const vo
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
-    cpm_launch(kLaunchNorm, kern, n_rows, threads, smem, stream, x, (const T*)delta, alpha, (const W*)w, (T*)y, rows, hidden, eps, write_back);
+    cpm_launch(kLaunchNorm, kern, n_rows, threads, smem, stream, x, (const T*)delta, (const T*)delta2, alpha, (const W*)w, (T*)y, rows, hidden,
+               eps, write_back);
     return launch_status();
 }
 
-CPM_API int cpm_add_rmsnorm(float* x, const void* delta, float alpha, const void* w, int w_is_f32, void* y,
+CPM_API int cpm_add_rmsnorm(float* x, const void* delta, const void* delta2, float alpha, const void* w, int w_is_f32, void* y,
                             const int* rows, int n_rows, int hidden, float eps, int write_back, int dtype,
                             cudaStream_t stream) {
     if (n_rows <= 0) return CPM_OK;
     if (dtype == CPM_BF16) {
-        if (w_is_f32) return launch_add_rmsnorm<bf16, float>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
-        return launch_add_rmsnorm<bf16, bf16>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+        if (w_is_f32) return launch_add_rmsnorm<bf16, float>(x, delta, delta2, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+        return launch_add_rmsnorm<bf16, bf16>(x, delta, delta2, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
     }
     if (!w_is_f32) return CPM_BAD_ARGUMENT;
-    return launch_add_rmsnorm<float, float>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+    return launch_add_rmsnorm<float, float>(x, delta, delta2, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
 }
 
 // x += alpha * delta, for a residual that no norm follows.

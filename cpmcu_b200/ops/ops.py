@@ -134,21 +134,26 @@ class Ops:
         return out
 
     def add_rmsnorm(self, x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float, weight: torch.Tensor,
-                    eps: float, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x fp32 [tokens, hidden] (+= alpha*delta, written back when rows is None) -> normed rows."""
+                    eps: float, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x fp32 [tokens, hidden] (+= alpha*delta, and + alpha*delta2 when a second addend is given; written back when
+        rows is None) -> normed rows."""
         self._f32(x, "residual stream")
         hidden = x.shape[-1]
         if delta is not None:
             self._act(delta, "residual addend")
             if delta.shape != x.shape:
                 raise ValueError(f"residual addend {tuple(delta.shape)} does not match the stream {tuple(x.shape)}")
+        if delta2 is not None:
+            self._act(delta2, "second residual addend")
+            if delta is None or delta2.shape != x.shape:
+                raise ValueError("a second residual addend goes with a first one of the stream's shape")
         if weight.dtype not in (torch.float32, self.dtype) or weight.numel() != hidden or weight.device.type != self.device.type:
             raise ValueError("norm weight: needs [hidden] in float32 or the compute dtype")
         n_rows = x.shape[0] if rows is None else rows.numel()
         if rows is not None:
             self._i32(rows, "norm rows")
         y = self.empty(n_rows, hidden)
-        check(self.lib.cpm_add_rmsnorm(_ptr(x), _ptr(delta), float(alpha), _ptr(weight),
+        check(self.lib.cpm_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(delta2), float(alpha), _ptr(weight),
                                        1 if weight.dtype == torch.float32 else 0, _ptr(y), _ptr(rows), n_rows,
                                        hidden, float(eps), 1 if rows is None else 0, self.code, self._stream()),
               f"rmsnorm (hidden {hidden})")

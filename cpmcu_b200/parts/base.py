@@ -282,6 +282,7 @@ class ResidualStream:
         self.ops = ops
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.pending2: Optional[torch.Tensor] = None       # a second output with the same factor (two sublayers side by side)
         self.pending_scale: float = 1.0
         # several streams per token: fp32 [tokens, streams, hidden], and the last sublayer's write still to be done
         # (its output, the mix matrix, the output weights), which the next read performs in the same pass
@@ -293,9 +294,11 @@ class ResidualStream:
         self.flush()
         self.copies = self.ops.hyper_fan_out(self.x, int(n_streams))
 
-    def add(self, delta: torch.Tensor, scale: float = 1.0) -> None:
+    def add(self, delta: torch.Tensor, scale: float = 1.0, second: Optional[torch.Tensor] = None) -> None:
+        """x += scale * delta (+ scale * second), deferred to the next norm's pass or the next ``flush``."""
         self.flush()
         self.pending = delta
+        self.pending2 = second
         self.pending_scale = float(scale)
 
     def flush(self) -> torch.Tensor:
@@ -306,7 +309,9 @@ class ResidualStream:
             return self.x
         if self.pending is not None:
             self.ops.residual_add(self.x, self.pending, self.pending_scale)
-            self.pending = None
+            if self.pending2 is not None:
+                self.ops.residual_add(self.x, self.pending2, self.pending_scale)
+            self.pending = self.pending2 = None
         return self.x
 
     def normed(self, norm: Norm, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -314,9 +319,14 @@ class ResidualStream:
             return norm.forward(self.flush(), rows)
         if self.pending is None:
             return norm.forward(self.x, rows)
-        y = norm.add_forward(self.x, self.pending, self.pending_scale, rows)
+        if self.pending2 is not None:
+            if not getattr(norm, "takes_two_addends", False):
+                return norm.forward(self.flush(), rows)
+            y = norm.add_forward(self.x, self.pending, self.pending_scale, rows, second=self.pending2)
+        else:
+            y = norm.add_forward(self.x, self.pending, self.pending_scale, rows)
         if rows is None:
-            self.pending = None
+            self.pending = self.pending2 = None
         return y
 
 

@@ -39,7 +39,7 @@ class PreNormResidualBlock(Block):
 class ParallelResidualBlock(Block):
     """x += s * (mixer(h) + feed_forward(h)) with h = norm(x): one norm, and both sublayers read its output.  The layer
     has no second norm (``feed_forward_norm`` is None); without a feed-forward it is x += s * mixer(norm(x)).  The two
-    outputs are added to the 32-bit stream one after the other, the second inside the next layer's norm kernel."""
+    outputs are added to the 32-bit stream one after the other inside the next layer's norm kernel."""
 
     recordable_prompt = True
 
@@ -53,9 +53,7 @@ class ParallelResidualBlock(Block):
         h = stream.normed(self.mixer_norm)
         a = self.mixer.forward(ctx, h, lane, writes_cache)
         f = self.feed_forward.forward(ctx, h) if self.feed_forward is not None else None
-        stream.add(a, self.residual_scale)
-        if f is not None:
-            stream.add(f, self.residual_scale)
+        stream.add(a, self.residual_scale, second=f)
 
 
 @BLOCKS.register("sandwich_norm_shift")

@@ -15,6 +15,7 @@ from .base import NORMS, Norm, WeightSpec
 @NORMS.register("rms_norm")
 class RMSNorm(Norm):
     recordable_prompt = True
+    takes_two_addends = True        # ``add_forward(..., second=)`` adds two deferred outputs in the norm's own pass
 
     def __init__(self, ops, hidden_size: int, eps: float, weight_name: str = "weight", offset: float = 0.0):
         """``weight_name``: the tensor's name below the part's prefix.  ``offset``: a constant added to the stored weight
@@ -42,8 +43,8 @@ class RMSNorm(Norm):
         return self.ops.add_rmsnorm(x, None, 0.0, self.weight, self.eps, rows)
 
     def add_forward(self, x: torch.Tensor, delta: torch.Tensor, scale: float,
-                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return self.ops.add_rmsnorm(x, delta, scale, self.weight, self.eps, rows)
+                    rows: Optional[torch.Tensor] = None, second: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.ops.add_rmsnorm(x, delta, scale, self.weight, self.eps, rows, delta2=second)
 
 
 @NORMS.register("layer_norm")
