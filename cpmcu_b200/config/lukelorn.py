@@ -13,7 +13,7 @@ feed-forward is dense or a mixture of experts.  A layer may run on another layer
     channel_delta:    mixer = {heads, kv_heads, dim, vdim, conv}   (the ranks of the decay's and the gate's first projections
                                are sizes of the checkpoint's tensors; ``decay_rank`` / ``gate_rank`` may state them)
     latent_attention: mixer = {heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, mask: {size}, rot: {dims, base}}
-    mlp = {kind: "dense", ff} | {kind: "moe", router: {experts, top}, expert: {ff}}
+    mlp = {kind: "dense", ff, act: "silu" (default) | "gelu_tanh"} | {kind: "moe", router: {experts, top}, expert: {ff}}
 """
 from __future__ import annotations
 
@@ -113,9 +113,13 @@ class LatentMixer:
 @dataclass(frozen=True)
 class DenseMlp:
     ff: int
+    act: str = "silu"                # the gate's activation: "silu" or "gelu_tanh"
 
     def to_json(self) -> Dict[str, Any]:
-        return {"kind": "dense", "ff": self.ff}
+        out = {"kind": "dense", "ff": self.ff}
+        if self.act != "silu":
+            out["act"] = self.act
+        return out
 
 
 @dataclass(frozen=True)
@@ -260,7 +264,7 @@ class LukelornConfig:
             if pr is not None:
                 what = pr.string("kind", choices=("dense", "moe"))
                 if what == "dense":
-                    mlp = DenseMlp(pr.integer("ff", minimum=1))
+                    mlp = DenseMlp(pr.integer("ff", minimum=1), pr.string("act", "silu", choices=("silu", "gelu_tanh")) or "silu")
                 elif what == "moe":
                     router, expert = pr.child("router"), pr.child("expert")
                     if router is None or expert is None:

@@ -68,7 +68,7 @@ def _feed_forward(cfg: LukelornConfig, p):
     if p is None:
         return None
     if isinstance(p, DenseMlp):
-        return PartSpec("gated_ffn", {"hidden_size": cfg.width, "intermediate_size": p.ff, "activation": "silu",
+        return PartSpec("gated_ffn", {"hidden_size": cfg.width, "intermediate_size": p.ff, "activation": p.act,
                                       "names": {"gate": "gate", "up": "up", "down": "down"}})
     if isinstance(p, MoeMlp):
         return PartSpec("routed_experts", {"hidden_size": cfg.width, "n_experts": p.experts, "top": p.top, "expert_size": p.expert_ff,

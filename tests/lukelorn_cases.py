@@ -50,8 +50,8 @@ def _moe(experts, top, ff):
     return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
 
 
-def _dense(ff):
-    return {"kind": "dense", "ff": ff}
+def _dense(ff, act=None):
+    return {"kind": "dense", "ff": ff, "act": act} if act else {"kind": "dense", "ff": ff}
 
 
 def _layer(mixer: dict, mlp: Optional[dict], weights_of: Optional[int] = None) -> dict:
@@ -88,7 +88,7 @@ def config_b() -> dict:
                 _layer(_attn(1, 1, 32, 16, 0.3, rot=(32, 100.0)), _moe(4, 1, 24)),
                 _layer(lat, None),
                 _layer(_delta(1, 1, 40, 72, 1, ranks=(1, 5)), _moe(3, 3, 8)),
-                _layer(_latent(2, 8, 2, 8, 8, 16, 1.1, window=1), _dense(40)),
+                _layer(_latent(2, 8, 2, 8, 8, 16, 1.1, window=1), _dense(40, "gelu_tanh")),
                 _layer(_attn(3, 3, 8, 8, 1.1, window=1, keep=3, cap=2.0), None),
             ]}
 

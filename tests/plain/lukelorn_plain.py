@@ -175,8 +175,9 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dic
     return torch.stack(out, dim=1).reshape(T, H * dv) @ w[p + "o"].T
 
 
-def dense_feed_forward(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+def dense_feed_forward(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, act: str = "silu") -> torch.Tensor:
+    gate = {"silu": silu, "gelu_tanh": gelu_tanh}[act]
+    return (gate(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict):
@@ -234,7 +235,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen: Optional[List
             raise ValueError(layer["type"])
         mlp = layer.get("mlp")
         if mlp is not None and mlp["kind"] == "dense":
-            a = a + dense_feed_forward(h, w, p + "mlp.")
+            a = a + dense_feed_forward(h, w, p + "mlp.", mlp.get("act", "silu"))
         elif mlp is not None:
             f, s, idx = mixture_of_experts(h, w, p + "mlp.", mlp, None if chosen is None else chosen[n_moe], slack)
             n_moe += 1

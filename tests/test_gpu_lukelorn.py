@@ -489,6 +489,31 @@ def test_rotation_of_adjacent_pairs_with_stretched_waves(dtype, d, rot, adjacent
     _close(keys, want[:, H], dtype, tol32=3e-5, tol16=1e-2)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["rotated", "plain"])
+def test_latent_attention_where_one_part_of_the_score_decides(folders, dtype, which):
+    """The latent layers alone, with the rotated part of queries and keys (or the plain part) scaled up so that it
+    decides the softmax: a rotation that paired other channels, a key part that lost its position or a window one token
+    off would move nearly all of a token's weight.  A prompt, then single tokens across the windows' edges."""
+    folder, cfg, w = folders("latent_attention")
+    w = {k: v.clone() for k, v in w.items()}
+    for i, layer in enumerate(cfg["layers"]):
+        m, p = layer["mixer"], f"l{i}.mix."
+        H, d, dr, R = m["heads"], m["dim"], m["rot_dim"], m["kv_rank"]
+        uq = w[p + "uq"].float().view(H, d + dr, -1)
+        if which == "rotated" and dr:
+            uq[:, d:] *= 6.0
+            w[p + "dkv"] = torch.cat([w[p + "dkv"][:R], (w[p + "dkv"][R:].float() * 6.0).bfloat16()])
+        elif which == "plain":
+            uq[:, :d] *= 6.0
+            w[p + "uk"] = (w[p + "uk"].float() * 4.0).bfloat16()
+        w[p + "uq"] = uq.reshape(H * (d + dr), -1).bfloat16()
+    import tempfile
+    folder = cases.write_folder(cfg, w, tempfile.mkdtemp(prefix=f"lukelorn-latent-{which}-"))
+    ids = cases.random_ids(cfg["vocab"], 160, 8)
+    run_and_check(make_stepper(folder, dtype), cfg, w, [ids], [[60, 2, 18] + [1] * 80], dtype, f"latent attention, {which} part scaled")
+
+
 @pytest.mark.parametrize("H,G,d,dv", [(3, 3, 16, 40), (6, 2, 40, 8), (2, 1, 70, 20), (4, 4, 64, 64), (2, 2, 128, 32)])
 def test_delta_rule_with_a_decay_per_key_channel(H, G, d, dv):
     """channel_decay and the recurrence (fp32) against the plain recurrence: one piece, and pieces for three sequences at
